@@ -3,3 +3,4 @@ from .base import (Architecture, ConfigError, RawConfig, register_architecture, 
 from .qwen3 import Qwen3Config
 from .vebonex import VebonexConfig
 from .tikizen import TikizenConfig
+from .sefalorn import SefalornConfig

@@ -11,16 +11,23 @@
 //
 // This is the kernel of the true 32-bit path and the fallback of the bfloat16 path
 // for head sizes that its tensor-core kernels do not take.
+//
+// Two options serve attention whose heads' scores are mixed before the softmax and penalised by distance.
+// JOINT: a query head holds one vector per key/value head, side by side (n_kv_heads * head_dim numbers), and its
+// score against a token is the sum of its products with all of the token's key heads; values are still those
+// of the head's own group.  dist_bias [n_heads, bias_len]: dist_bias[h, pos - j] is taken off head h's score
+// against key j (a distance beyond the table reads its last entry).
 #include "common.cuh"
 
 #define ATT_WARPS 4
 
-template <int DPL>  // value elements per lane: v_dim <= 32 * DPL
+template <int DPL, bool JOINT>  // DPL value elements per lane: v_dim <= 32 * DPL
 __global__ void paged_attention_generic_kernel(
     const act_t* __restrict__ q, const act_t* __restrict__ k_pages, const act_t* __restrict__ v_pages,
     const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
     const int* __restrict__ row_request, const int* __restrict__ positions, int n_heads, int n_kv_heads,
-    int head_dim, int v_dim, float scale, int window, act_t* __restrict__ out) {
+    int head_dim, int v_dim, float scale, int window, act_t* __restrict__ out,
+    const float* __restrict__ dist_bias, int bias_len) {
     extern __shared__ float smem[];
     ib_grid_dependency_sync();
     const int row = blockIdx.x;
@@ -28,15 +35,17 @@ __global__ void paged_attention_generic_kernel(
     const int head = blockIdx.y * ATT_WARPS + warp;
     if (head >= n_heads) return;  // whole warps leave; only warp-level syncs follow
     const int d = head_dim;
-    float* qs = smem + warp * d;
+    const int dq = JOINT ? n_kv_heads * d : d;      // numbers of a query head
+    float* qs = smem + warp * dq;
     const int pos = positions[row];
     const int req = row_request[row];
     const int lo = ib_first_visible(pos, window);
     const int kvh = head / (n_heads / n_kv_heads);
     const int* bt = block_table + (long)req * max_pages;
 
-    const act_t* qr = q + ((long)row * n_heads + head) * d;
-    for (int e = lane; e < d; e += 32) qs[e] = ib_to_float(qr[e]);
+    const act_t* qr = q + ((long)row * n_heads + head) * dq;
+    for (int e = lane; e < dq; e += 32) qs[e] = ib_to_float(qr[e]);
+    const float* bias_h = dist_bias ? dist_bias + (long)head * bias_len : nullptr;
     __syncwarp();
 
     float acc[DPL];
@@ -53,10 +62,19 @@ __global__ void paged_attention_generic_kernel(
             const int page = bt[j / page_size];
             if (page >= 0 && page < n_pages) {
                 off = ((long)page * n_kv_heads + kvh) * page_size + (j % page_size);
-                const act_t* kr = k_pages + off * d;
                 float dot = 0.0f;
-                for (int e = 0; e < d; ++e) dot = fmaf(qs[e], ib_to_float(kr[e]), dot);
+                if (JOINT) {
+                    for (int c = 0; c < n_kv_heads; ++c) {
+                        const act_t* kr = k_pages + (((long)page * n_kv_heads + c) * page_size + (j % page_size)) * d;
+                        const float* qc = qs + c * d;
+                        for (int e = 0; e < d; ++e) dot = fmaf(qc[e], ib_to_float(kr[e]), dot);
+                    }
+                } else {
+                    const act_t* kr = k_pages + off * d;
+                    for (int e = 0; e < d; ++e) dot = fmaf(qs[e], ib_to_float(kr[e]), dot);
+                }
                 s = dot * scale;
+                if (bias_h) s -= bias_h[pos - j < bias_len ? pos - j : bias_len - 1];
             }
         }
         const float m_new = fmaxf(m, ib_warp_max(s));
@@ -92,23 +110,28 @@ IB_EXPORT int ib_paged_attention_generic(const void* q, const void* k_pages, con
                                          const int* block_table, int max_pages, int page_size, int n_pages,
                                          const int* row_request, const int* positions, int n_rows, int n_heads,
                                          int n_kv_heads, int head_dim, int v_dim, float scale, int window, void* out,
-                                         cudaStream_t stream) {
+                                         int joint, const float* dist_bias, int bias_len, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim <= 0 || page_size <= 0 || max_pages <= 0)
         return IB_ERR_ARGUMENT;
     if (v_dim <= 0) return IB_ERR_ARGUMENT;
-    if (head_dim > 512 || v_dim > 512) return IB_ERR_UNSUPPORTED;
+    if (dist_bias != nullptr && bias_len <= 0) return IB_ERR_ARGUMENT;
+    const int dq = joint ? n_kv_heads * head_dim : head_dim;
+    if (head_dim > 512 || v_dim > 512 || dq > 2048) return IB_ERR_UNSUPPORTED;
     const dim3 grid(n_rows, (n_heads + ATT_WARPS - 1) / ATT_WARPS);
-    const size_t smem = (size_t)ATT_WARPS * head_dim * sizeof(float);
-#define IB_LAUNCH_ATT(DPL)                                                                                      \
-    ib_launch(paged_attention_generic_kernel<DPL>, grid, 32 * ATT_WARPS, smem, stream,                          \
+    const size_t smem = (size_t)ATT_WARPS * dq * sizeof(float);
+#define IB_LAUNCH_ATT_J(DPL, JOINT)                                                                             \
+    ib_launch(paged_attention_generic_kernel<DPL, JOINT>, grid, 32 * ATT_WARPS, smem, stream,                   \
         (const act_t*)q, (const act_t*)k_pages, (const act_t*)v_pages, block_table, max_pages, page_size,       \
-        n_pages, row_request, positions, n_heads, n_kv_heads, head_dim, v_dim, scale, window, (act_t*)out)
+        n_pages, row_request, positions, n_heads, n_kv_heads, head_dim, v_dim, scale, window, (act_t*)out,      \
+        dist_bias, bias_len)
+#define IB_LAUNCH_ATT(DPL) do { if (joint) IB_LAUNCH_ATT_J(DPL, true); else IB_LAUNCH_ATT_J(DPL, false); } while (0)
     if (v_dim <= 32) IB_LAUNCH_ATT(1);
     else if (v_dim <= 64) IB_LAUNCH_ATT(2);
     else if (v_dim <= 128) IB_LAUNCH_ATT(4);
     else if (v_dim <= 256) IB_LAUNCH_ATT(8);
     else IB_LAUNCH_ATT(16);
 #undef IB_LAUNCH_ATT
+#undef IB_LAUNCH_ATT_J
     return ib_launch_status();
 }

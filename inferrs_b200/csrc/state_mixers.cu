@@ -125,10 +125,11 @@ IB_EXPORT int ib_scaled_add_norm(float* residual, const void* delta, float alpha
 // Up to three slices of a projection's rows as float: slice s is n_heads[s] heads of dim[s] numbers from column
 // src_col[s] on, written from column dst_col[s] of the float rows; where rotate[s] is set the first rot_dim of
 // each head turn by the row's position (element i with i + rot_dim / 2; tables [positions, rot_dim / 2]); every
-// number is multiplied by scale[s].
+// number is multiplied by scale[s]; where silu[s] is set the number goes through silu first (a slice is rotated or
+// goes through silu, not both).
 // ---------------------------------------------------------------------------
 struct HeadSlices {
-    int n, src_col[3], dst_col[3], n_heads[3], dim[3], rotate[3];
+    int n, src_col[3], dst_col[3], n_heads[3], dim[3], rotate[3], silu[3];
     float scale[3];
 };
 
@@ -156,11 +157,13 @@ __global__ void heads_to_float_kernel(const act_t* __restrict__ src, long ld, He
         const float c = cos_table[(long)pos * half + i], sn = sin_table[(long)pos * half + i];
         v = j < half ? v * c - ib_to_float(h[j + half]) * sn : v * c + ib_to_float(h[j - half]) * sn;
     }
+    if (P.silu[s]) v = sm_silu(v);
     dst[(long)row * dst_ld + P.dst_col[s] + idx] = v * P.scale[s];
 }
 
 IB_EXPORT int ib_heads_to_float(const void* src, long ld, int n_slices, const int* src_col, const int* dst_col,
-                                const int* n_heads, const int* dim, const int* rotate, const float* scale, float* dst,
+                                const int* n_heads, const int* dim, const int* rotate, const int* silu,
+                                const float* scale, float* dst,
                                 long dst_ld, const float* cos_table, const float* sin_table, int rot_dim, int table_rows,
                                 const int* positions, int n_rows, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
@@ -171,8 +174,9 @@ IB_EXPORT int ib_heads_to_float(const void* src, long ld, int n_slices, const in
     int total = 0;
     for (int s = 0; s < n_slices; ++s) {
         P.src_col[s] = src_col[s]; P.dst_col[s] = dst_col[s]; P.n_heads[s] = n_heads[s]; P.dim[s] = dim[s];
-        P.rotate[s] = rotate[s]; P.scale[s] = scale[s];
-        if (n_heads[s] <= 0 || dim[s] <= 0 || (rotate[s] && rot_dim > dim[s])) return IB_ERR_ARGUMENT;
+        P.rotate[s] = rotate[s]; P.scale[s] = scale[s]; P.silu[s] = silu ? silu[s] : 0;
+        if (n_heads[s] <= 0 || dim[s] <= 0 || (rotate[s] && rot_dim > dim[s]) || (rotate[s] && P.silu[s]))
+            return IB_ERR_ARGUMENT;
         if (rotate[s] && rot_dim > 0 && (cos_table == nullptr || sin_table == nullptr || positions == nullptr ||
                                         table_rows <= 0))
             return IB_ERR_ARGUMENT;
@@ -186,12 +190,13 @@ IB_EXPORT int ib_heads_to_float(const void* src, long ld, int n_slices, const in
 }
 
 // ---------------------------------------------------------------------------
-// Channel c < C of row r:  out[r, c] = silu(bias[c] + sum_j w[c, j] * input(r - (taps - 1 - j), c)),
+// Channel c < C of row r:  out[r, c] = silu(bias[c] + sum_j w[c, j] * input(r - (taps - 1 - j), c))  (bias may be absent),
 // where input(t, c) is the projection's column conv_col + c of row t if t is a row of the same request in this
 // step, and else what the request's state keeps: its last taps - 1 inputs, oldest first, [taps - 1, C] floats at
 // conv_state_off of its slot (zeros for a new request: nothing stands before the start).
 // Head h of row r (threads C .. C + H - 1):  dt = softplus(proj[r, dt_col + h] + dt_bias[h]),
-// gates[r, h] = exp(-exp(a_log[h]) dt)  (what the state keeps),  gates[r, H + h] = dt  (what the input is taken by).
+// gates[r, h] = exp(-exp(a_log[h]) dt)  (what the state keeps),  gates[r, H + h] = dt  (what the input is taken by);
+// with beta_col >= 0 the second is sigmoid(proj[r, beta_col + h]) instead (the step size of a delta rule).
 // ---------------------------------------------------------------------------
 __global__ void conv_silu_gates_kernel(const act_t* __restrict__ proj, long ld, int conv_col, int C, int taps,
                                        const float* __restrict__ w, const float* __restrict__ bias,
@@ -199,7 +204,7 @@ __global__ void conv_silu_gates_kernel(const act_t* __restrict__ proj, long ld, 
                                        const int* __restrict__ q_start, const int* __restrict__ slots,
                                        const int* __restrict__ row_request, float* __restrict__ out, int dt_col, int H,
                                        const float* __restrict__ dt_bias, const float* __restrict__ a_log,
-                                       float* __restrict__ gates) {
+                                       float* __restrict__ gates, int beta_col) {
     ib_grid_dependency_sync();
     const int row = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -209,13 +214,13 @@ __global__ void conv_silu_gates_kernel(const act_t* __restrict__ proj, long ld, 
         const int h = c - C;
         const float dt = sm_softplus(ib_to_float(in[dt_col + h]) + dt_bias[h]);
         gates[(long)row * 2 * H + h] = expf(-expf(a_log[h]) * dt);
-        gates[(long)row * 2 * H + H + h] = dt;
+        gates[(long)row * 2 * H + H + h] = beta_col >= 0 ? sm_sigmoid(ib_to_float(in[beta_col + h])) : dt;
         return;
     }
     const int req = row_request[row];
     const int row0 = q_start[req];
     const float* kept = state + (long)slots[req] * slot_stride + conv_state_off;
-    float acc = bias[c];
+    float acc = bias ? bias[c] : 0.0f;
     for (int j = 0; j < taps; ++j) {
         const int t = row - (taps - 1 - j);
         float v;
@@ -229,10 +234,10 @@ __global__ void conv_silu_gates_kernel(const act_t* __restrict__ proj, long ld, 
 IB_EXPORT int ib_conv_silu_gates(const void* proj, long ld, int conv_col, int C, int taps, const float* w,
                                  const float* bias, const float* state, long slot_stride, long conv_state_off,
                                  const int* q_start, const int* slots, const int* row_request, float* out, int dt_col,
-                                 int H, const float* dt_bias, const float* a_log, float* gates, int n_rows,
-                                 cudaStream_t stream) {
+                                 int H, const float* dt_bias, const float* a_log, float* gates, int beta_col,
+                                 int n_rows, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
-    if (C <= 0 || taps <= 0 || H <= 0 || proj == nullptr || w == nullptr || bias == nullptr || state == nullptr ||
+    if (C <= 0 || taps <= 0 || H <= 0 || proj == nullptr || w == nullptr || state == nullptr ||
         out == nullptr || gates == nullptr || dt_bias == nullptr || a_log == nullptr ||
         slot_stride < conv_state_off + (long)(taps - 1) * C)
         return IB_ERR_ARGUMENT;
@@ -240,7 +245,7 @@ IB_EXPORT int ib_conv_silu_gates(const void* proj, long ld, int conv_col, int C,
     const int threads = 128;
     ib_launch(conv_silu_gates_kernel, dim3((C + H + threads - 1) / threads, n_rows), threads, 0, stream,
               (const act_t*)proj, ld, conv_col, C, taps, w, bias, state, slot_stride, conv_state_off, q_start, slots,
-              row_request, out, dt_col, H, dt_bias, a_log, gates);
+              row_request, out, dt_col, H, dt_bias, a_log, gates, beta_col);
     return ib_launch_status();
 }
 
@@ -394,12 +399,15 @@ IB_EXPORT int ib_clamped_gate(const void* gate_up, void* out, int n_rows, int in
 
 // ---------------------------------------------------------------------------
 // Router.  logits [rows, ld] float hold n_experts router logits per row (and, with has_shared, one more column:
-// the shared expert's gate).  weights[r, e] = softmax over the `top` largest of logits[r, :] + bias among
-// themselves for those experts, 0 for the others (equal logits: the lower index wins);
+// the shared expert's gate).  mode 0: weights[r, e] = softmax over the `top` largest of logits[r, :] + bias among
+// themselves for those experts, 0 for the others (equal logits: the lower index wins).  mode 1: the scores are
+// s = sigmoid(logits + bias), the `top` largest scores are chosen (equal scores: the lower index) and
+// weights[r, e] = s_e / (sum of the chosen scores + 1e-20).  Either way the weights are multiplied by `scale`;
 // weights[r, n_experts] = sigmoid(logits[r, n_experts]).  One warp per row.
 // ---------------------------------------------------------------------------
 __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, const float* __restrict__ bias,
-                                   int n_experts, int top, int has_shared, float* __restrict__ weights, int n_rows) {
+                                   int n_experts, int top, int has_shared, float* __restrict__ weights, int n_rows,
+                                   int mode, float scale) {
     ib_grid_dependency_sync();
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -414,7 +422,8 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, co
         float best = -INFINITY;
         int at = 0x7fffffff;
         for (int e = lane; e < n_experts; e += 32) {
-            const float v = z[e] + (bias ? bias[e] : 0.0f);
+            float v = z[e] + (bias ? bias[e] : 0.0f);
+            if (mode == 1) v = sm_sigmoid(v);
             if (w[e] == 0.0f && (v > best || (v == best && e < at))) { best = v; at = e; }
         }
 #pragma unroll
@@ -425,24 +434,27 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, co
         }
         if (at == 0x7fffffff) break;        // fewer experts than `top`, or nothing but NaN
         if (k == 0) first = best;
-        sum += expf(best - first);
+        sum += mode == 1 ? best : expf(best - first);
         if (lane == 0) w[at] = -1.0f;
         __syncwarp();
     }
     for (int e = lane; e < n_experts; e += 32)
-        if (w[e] < 0.0f) w[e] = expf(z[e] + (bias ? bias[e] : 0.0f) - first) / sum;
+        if (w[e] < 0.0f) {
+            const float v = z[e] + (bias ? bias[e] : 0.0f);
+            w[e] = (mode == 1 ? sm_sigmoid(v) / (sum + 1e-20f) : expf(v - first) / sum) * scale;
+        }
     if (has_shared && lane == 0) w[n_experts] = sm_sigmoid(z[n_experts]);
 }
 
 IB_EXPORT int ib_router_topk(const float* logits, long ld, const float* bias, int n_experts, int top, int has_shared,
-                             float* weights, int n_rows, cudaStream_t stream) {
+                             float* weights, int n_rows, int mode, float scale, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
-    if (n_experts <= 0 || top <= 0 || top > n_experts || logits == nullptr || weights == nullptr ||
+    if (n_experts <= 0 || top <= 0 || top > n_experts || logits == nullptr || weights == nullptr || mode < 0 || mode > 1 ||
         ld < n_experts + (has_shared ? 1 : 0))
         return IB_ERR_ARGUMENT;
     const int warps = 4;
     ib_launch(router_topk_kernel, (n_rows + warps - 1) / warps, 32 * warps, 0, stream, logits, ld, bias, n_experts, top,
-              has_shared ? 1 : 0, weights, n_rows);
+              has_shared ? 1 : 0, weights, n_rows, mode, scale);
     return ib_launch_status();
 }
 

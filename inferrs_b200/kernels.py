@@ -38,7 +38,8 @@ _SIGNATURES = {
                               c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_void_p, c_void_p, c_void_p, c_void_p],
     "ib_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
-                                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                                   c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_int,
+                                   c_void_p],
     "ib_gemm_tn_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
                         c_long, c_void_p],
     "ib_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -82,14 +83,22 @@ _SIGNATURES = {
                                 c_long, c_int, c_long, c_long, c_long, c_void_p],
     "ib_scaled_add_norm": [c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p],
     "ib_heads_to_float": [c_void_p, c_long, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                          c_long, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
+                          c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
     "ib_conv_silu_gates": [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_long, c_long, c_void_p,
-                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "ib_conv_state_shift": [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_long, c_long, c_void_p, c_void_p, c_int,
                             c_void_p],
     "ib_gate_group_norm": [c_void_p, c_void_p, c_long, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
     "ib_clamped_gate": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p],
-    "ib_router_topk": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "ib_router_topk": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
+    "ib_gated_add_layer_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                                c_int, c_void_p],
+    "ib_gated_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "ib_bias_add": [c_void_p, c_long, c_void_p, c_int, c_int, c_void_p],
+    "ib_scaled_sum": [c_void_p, c_float, c_void_p, c_float, c_void_p, c_long, c_void_p],
+    "ib_mix_queries": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "ib_delta_scan": [c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_long, c_float, c_float,
+                      c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ib_routed_gate": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
     "ib_decay_scan": [c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p,
                       c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -604,9 +613,14 @@ def span_argument(window: Optional[int], chunk: Optional[int] = None) -> int:
 
 def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                             row_request: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
-                            out: torch.Tensor):
+                            out: torch.Tensor, joint: bool = False, dist_bias: Optional[torch.Tensor] = None):
     """out[r, h*dv:(h+1)*dv] = attention of token r's head h over its request's cached keys lo..pos.  ``window``:
-    see :func:`span_argument` (a negative number: chunks).  Values may have another size dv than keys."""
+    see :func:`span_argument` (a negative number: chunks).  Values may have another size dv than keys.
+
+    ``joint``: ``q`` is [rows, H, kv_heads * d], one vector per key/value head side by side, and a score is the sum
+    of its products with all key heads of the token (the form that queries mixed by :func:`mix_queries` take).
+    ``dist_bias`` float32 [H, L]: dist_bias[h, pos - j] is taken off head h's score against key j (a distance beyond
+    the table reads its last entry)."""
     act = out.dtype
     _need(q, "q", (act,), 3)
     _need(k_pages, "k_pages", (act,), 4)
@@ -615,17 +629,22 @@ def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     _need(row_request, "row_request", _I, 1)
     _need(positions, "positions", _I, 1)
     _need(out, "out", _W, 2)
-    n, nh, d = q.shape
+    _need(dist_bias, "dist_bias", (torch.float32,), 2, optional=True)
+    n, nh, dq = q.shape
     n_pages, nkv, page_size, dk = k_pages.shape
     dv = v_pages.shape[3]
-    if dk != d or v_pages.shape[:3] != k_pages.shape[:3] or out.shape != (n, nh * dv) or nh % nkv:
+    d = dq // nkv if joint else dq
+    if dk != d or (joint and dq != nkv * dk) or v_pages.shape[:3] != k_pages.shape[:3] or out.shape != (n, nh * dv) \
+            or nh % nkv or (dist_bias is not None and (dist_bias.shape[0] != nh or dist_bias.shape[1] < 1)):
         raise KernelError(f"paged_attention: q {tuple(q.shape)}, pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)}, "
                           f"out {tuple(out.shape)}")
-    if d > 512 or dv > 512:
-        raise KernelError(f"paged_attention: head sizes {d}, {dv} are larger than 512, the largest the kernel takes")
+    if d > 512 or dv > 512 or dq > 2048:
+        raise KernelError(f"paged_attention: head sizes {dq}, {dv} are larger than the kernel takes (512, or 2048 for "
+                          f"joint queries)")
     _check(_core(act).ib_paged_attention_generic(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(row_request),
-        _p(positions), n, nh, nkv, d, dv, float(scale), int(window) if window else 0, _p(out), _stream()),
+        _p(positions), n, nh, nkv, d, dv, float(scale), int(window) if window else 0, _p(out), int(bool(joint)),
+        _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[1], _stream()),
         "paged_attention_generic")
 
 
@@ -899,7 +918,8 @@ def heads_to_float(src: torch.Tensor, slices, dst: torch.Tensor, cos: Optional[t
     """Up to three slices of a projection's rows as float32.  ``slices``: (first column in ``src``, first column in
     ``dst``, heads, numbers per head, rotate?, scale) each; a rotated slice has the first ``rot_dim`` numbers of each
     head turned by the row's position (element i with i + rot_dim / 2; float32 tables [positions, rot_dim / 2]); every
-    number is multiplied by the slice's scale."""
+    number is multiplied by the slice's scale.  A slice may carry a seventh entry: true sends its numbers through silu
+    first (such a slice is not rotated)."""
     act = src.dtype
     _need(src, "src", _W, 2)
     _need(dst, "dst", (torch.float32,), 2)
@@ -915,45 +935,53 @@ def heads_to_float(src: torch.Tensor, slices, dst: torch.Tensor, cos: Optional[t
         if cos.shape[1] != rot_dim // 2 or sin.shape != cos.shape or positions.shape[0] != n:
             raise KernelError(f"heads_to_float: rotation tables {tuple(cos.shape)} do not match rot_dim {rot_dim}")
         table_rows = cos.shape[0]
-    for a, b, heads, dim, rot, _scale in slices:
+    for a, b, heads, dim, rot, _scale in (sl[:6] for sl in slices):
         if a < 0 or b < 0 or a + heads * dim > src.shape[1] or b + heads * dim > dst.shape[1] or (rot and rot_dim > dim):
             raise KernelError(f"heads_to_float: slice {(a, b, heads, dim)} does not fit src {tuple(src.shape)}, dst "
                               f"{tuple(dst.shape)}")
     k = len(slices)
     ints = [(c_int * k)(*[int(sl[i]) for sl in slices]) for i in range(5)]
+    silu = (c_int * k)(*[int(bool(sl[6])) if len(sl) > 6 else 0 for sl in slices])
+    if any(s and sl[4] for s, sl in zip(silu, slices)):
+        raise KernelError("heads_to_float: a slice is rotated or goes through silu, not both")
     scales = (c_float * k)(*[float(sl[5]) for sl in slices])
     _check(_core(act).ib_heads_to_float(
-        _p(src), src.shape[1], k, ints[0], ints[1], ints[2], ints[3], ints[4], scales, _p(dst), dst.shape[1],
+        _p(src), src.shape[1], k, ints[0], ints[1], ints[2], ints[3], ints[4], silu, scales, _p(dst), dst.shape[1],
         _p(cos) if turning else None, _p(sin) if turning else None, int(rot_dim) if turning else 0, table_rows,
         _p(positions) if turning else None, n, _stream()), "heads_to_float")
 
 
-def conv_silu_gates(proj: torch.Tensor, conv_col: int, conv_w: torch.Tensor, conv_b: torch.Tensor, state: torch.Tensor,
-                    conv_state_off: int, q_start: torch.Tensor, slots: torch.Tensor, row_request: torch.Tensor,
-                    out: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, gates: torch.Tensor):
+def conv_silu_gates(proj: torch.Tensor, conv_col: int, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor],
+                    state: torch.Tensor, conv_state_off: int, q_start: torch.Tensor, slots: torch.Tensor,
+                    row_request: torch.Tensor, out: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                    gates: torch.Tensor, beta_col: Optional[int] = None):
     """out[r, c] = silu(b[c] + sum_j w[c, j] * input(r - (taps - 1 - j), c)) for the C channels from column
     ``conv_col`` of ``proj``; an input before the request's first row of the step comes from its state (the last
     taps - 1 inputs, oldest first, [taps - 1, C] float32 from ``conv_state_off`` of its slot).  And per head,
-    dt = softplus(proj[r, dt_col + h] + dt_bias[h]): gates[r, h] = exp(-exp(a_log[h]) dt), gates[r, H + h] = dt."""
+    dt = softplus(proj[r, dt_col + h] + dt_bias[h]): gates[r, h] = exp(-exp(a_log[h]) dt), gates[r, H + h] = dt, or,
+    with ``beta_col``, sigmoid(proj[r, beta_col + h]) (the step size of a delta rule).  ``conv_b`` None: no bias."""
     act = proj.dtype
     _need(proj, "proj", _W, 2)
-    for name, t, nd in (("conv_w", conv_w, 2), ("conv_b", conv_b, 1), ("dt_bias", dt_bias, 1), ("a_log", a_log, 1),
+    for name, t, nd in (("conv_w", conv_w, 2), ("dt_bias", dt_bias, 1), ("a_log", a_log, 1),
                         ("out", out, 2), ("gates", gates, 2)):
         _need(t, name, (torch.float32,), nd)
+    _need(conv_b, "conv_b", (torch.float32,), 1, optional=True)
     _need(state, "state", (torch.float32,))
     for name, t in (("q_start", q_start), ("slots", slots), ("row_request", row_request)):
         _need(t, name, _I, 1)
     n, ld = proj.shape
     channels, taps = conv_w.shape
     heads = dt_bias.shape[0]
-    if out.shape != (n, channels) or gates.shape != (n, 2 * heads) or conv_b.shape[0] != channels \
+    if out.shape != (n, channels) or gates.shape != (n, 2 * heads) \
+            or (conv_b is not None and conv_b.shape[0] != channels) \
+            or (beta_col is not None and not 0 <= beta_col <= ld - heads) \
             or a_log.shape[0] != heads or conv_col + channels > ld or dt_col + heads > ld or row_request.shape[0] != n:
         raise KernelError(f"conv_silu_gates: proj {tuple(proj.shape)}, conv {tuple(conv_w.shape)}, out "
                           f"{tuple(out.shape)}, gates {tuple(gates.shape)}")
     _check(_core(act).ib_conv_silu_gates(
         _p(proj), ld, int(conv_col), channels, taps, _p(conv_w), _p(conv_b), _p(state), state[0].numel(),
         int(conv_state_off), _p(q_start), _p(slots), _p(row_request), _p(out), int(dt_col), heads, _p(dt_bias),
-        _p(a_log), _p(gates), n, _stream()), "conv_silu_gates")
+        _p(a_log), _p(gates), -1 if beta_col is None else int(beta_col), n, _stream()), "conv_silu_gates")
 
 
 def conv_state_shift(proj: torch.Tensor, conv_col: int, channels: int, taps: int, state: torch.Tensor,
@@ -1001,10 +1029,16 @@ def clamped_gate(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: 
            "clamped_gate")
 
 
+ROUTE_SOFTMAX_OF_CHOSEN, ROUTE_SIGMOID_SHARE = 0, 1
+
+
 def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], n_experts: int, top: int, has_shared: bool,
-                weights: torch.Tensor, act_dtype: torch.dtype):
+                weights: torch.Tensor, act_dtype: torch.dtype, mode: int = ROUTE_SOFTMAX_OF_CHOSEN, scale: float = 1.0):
     """weights[r, e] = the softmax over the ``top`` largest of logits[r, :n_experts] + bias, among themselves, for
-    those experts and 0 for the others; with ``has_shared`` weights[r, n_experts] = sigmoid(logits[r, n_experts])."""
+    those experts and 0 for the others; with ``has_shared`` weights[r, n_experts] = sigmoid(logits[r, n_experts]).
+    ``mode`` ROUTE_SIGMOID_SHARE: the scores are sigmoid(logits + bias), the ``top`` largest are chosen and each
+    chosen expert weighs its score over the sum of the chosen scores (+ 1e-20).  The routed weights are multiplied by
+    ``scale``."""
     _need(logits, "logits", (torch.float32,), 2)
     _need(bias, "bias", (torch.float32,), 1, optional=True)
     _need(weights, "weights", (torch.float32,), 2)
@@ -1014,8 +1048,11 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], n_experts: i
             or not 0 < top <= n_experts:
         raise KernelError(f"router_topk: logits {tuple(logits.shape)}, weights {tuple(weights.shape)}, top {top} of "
                           f"{n_experts}")
+    if mode not in (ROUTE_SOFTMAX_OF_CHOSEN, ROUTE_SIGMOID_SHARE):
+        raise KernelError(f"router_topk: unknown mode {mode}")
     _check(_core(act_dtype).ib_router_topk(_p(logits), logits.shape[1], _p(bias), int(n_experts), int(top),
-                                           int(bool(has_shared)), _p(weights), n, _stream()), "router_topk")
+                                           int(bool(has_shared)), _p(weights), n, int(mode), float(scale), _stream()),
+           "router_topk")
 
 
 def routed_gate(gate_up: torch.Tensor, weights: torch.Tensor, n_experts: int, ff: int, out: torch.Tensor):
@@ -1080,6 +1117,116 @@ def decay_scan(x: torch.Tensor, q_col: int, k_col: int, v_col: int, groups: int,
         _p(x), x.shape[1], int(q_col), int(k_col), int(v_col), int(groups), keep_p, keep_ld, take_p, take_ld, _p(skip),
         _p(state), state[0].numel(), _p(q_start), _p(slots), int(n_requests), _p(out), heads, d_dim, e_dim,
         int(max_rows), _stream()), "decay_scan")
+
+
+def delta_scan(x: torch.Tensor, q_col: int, k_col: int, v_col: int, groups: int, fade: torch.Tensor,
+               beta: torch.Tensor, unit_eps: Optional[float], q_scale: float, state: torch.Tensor,
+               q_start: torch.Tensor, slots: torch.Tensor, n_requests: int, out: torch.Tensor, key_dim: int,
+               act_dtype: torch.dtype, max_rows: int = 0):
+    """The gated delta rule over each request's rows in float32: S = fade S; u = beta (v - S^T k); S = S + k u^T;
+    o = S^T q.
+
+    ``x`` float32 [rows, ld] holds q and k as [groups, D] and v as [H, E] from the given columns on (head h reads
+    group h / (H / groups)); ``fade`` and ``beta`` are [rows, H] views with unit last stride; ``unit_eps`` not None:
+    q and k are divided by sqrt(sum of squares + unit_eps) per head; q is multiplied by ``q_scale``; ``out`` float32
+    [rows, H, E]; ``state`` float32 [slots, ...] with at least H*D*E numbers per slot, S first.  ``max_rows``: the
+    most rows that a request brings, if the caller knows (1: the form for steps of single tokens)."""
+    _need(x, "x", (torch.float32,), 2)
+    _need(out, "out", (torch.float32,), 3)
+    _need(state, "state", (torch.float32,))
+    _need(q_start, "q_start", _I, 1)
+    _need(slots, "slots", _I, 1)
+    n, heads, e_dim = out.shape
+    d_dim = int(key_dim)
+    for name, t in (("fade", fade), ("beta", beta)):
+        if not (t.is_cuda and t.dtype == torch.float32 and t.dim() == 2 and t.shape == (n, heads) and t.stride(1) == 1):
+            raise KernelError(f"delta_scan: {name} must be a float32 [rows, H] CUDA view with unit last stride")
+    if x.shape[0] != n or groups <= 0 or heads % groups or d_dim <= 0 \
+            or max(q_col, k_col) + groups * d_dim > x.shape[1] or v_col + heads * e_dim > x.shape[1] \
+            or q_start.shape[0] < n_requests + 1 or slots.shape[0] < n_requests \
+            or state[0].numel() < heads * d_dim * e_dim:
+        raise KernelError(f"delta_scan: x {tuple(x.shape)}, out {tuple(out.shape)}, {groups} groups of {d_dim}")
+    if d_dim > 256:
+        raise KernelError(f"delta_scan: {d_dim} key channels per head are more than the kernel's 256")
+    _check(_core(act_dtype).ib_delta_scan(
+        _p(x), x.shape[1], int(q_col), int(k_col), int(v_col), int(groups), fade.data_ptr(), fade.stride(0),
+        beta.data_ptr(), beta.stride(0), -1.0 if unit_eps is None else float(unit_eps), float(q_scale), _p(state),
+        state[0].numel(), _p(q_start), _p(slots), int(n_requests), _p(out), heads, d_dim, e_dim, int(max_rows),
+        _stream()), "delta_scan")
+
+
+def gated_add_layer_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], gate_pre: Optional[torch.Tensor],
+                         gate_bias: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out: torch.Tensor,
+                         rows: Optional[torch.Tensor] = None):
+    """residual <- residual + sigmoid(gate_pre + gate_bias) * delta (float32, in place; without ``gate_pre`` the
+    delta is added as it is, without ``delta`` nothing), then out = (x - mean) / sqrt(variance + eps) * weight in the
+    activation dtype.  With ``rows`` only those rows are read and the stream is left as it is."""
+    act = out.dtype
+    _need(residual, "residual", (torch.float32,), 2)
+    _need(delta, "delta", (act,), 2, optional=True)
+    _need(gate_pre, "gate_pre", (act,), 2, optional=True)
+    _need(gate_bias, "gate_bias", (torch.float32,), 1, optional=True)
+    _need(weight, "weight", (torch.float32,), 1)
+    _need(out, "out", _W, 2)
+    _need(rows, "rows", _I, 1, optional=True)
+    n, width = residual.shape
+    n_out = n if rows is None else rows.shape[0]
+    if out.shape != (n_out, width) or weight.shape[0] != width or (delta is not None and delta.shape != (n, width)) \
+            or (gate_pre is not None and (delta is None or gate_pre.shape != (n, width))) \
+            or (gate_bias is not None and gate_bias.shape[0] != width):
+        raise KernelError(f"gated_add_layer_norm: residual {tuple(residual.shape)}, out {tuple(out.shape)}, delta "
+                          f"{None if delta is None else tuple(delta.shape)}")
+    _check(_core(act).ib_gated_add_layer_norm(_p(residual), _p(delta), _p(gate_pre), _p(gate_bias), _p(weight),
+                                              float(eps), _p(out), _p(rows), n_out, width, _stream()),
+           "gated_add_layer_norm")
+
+
+def gated_rows(delta: torch.Tensor, gate_pre: torch.Tensor, gate_bias: Optional[torch.Tensor], out: torch.Tensor):
+    """out = delta * sigmoid(gate_pre + gate_bias), all [rows, width] in the activation dtype."""
+    act = out.dtype
+    _need(delta, "delta", (act,), 2)
+    _need(gate_pre, "gate_pre", (act,), 2)
+    _need(gate_bias, "gate_bias", (torch.float32,), 1, optional=True)
+    _need(out, "out", _W, 2)
+    if delta.shape != out.shape or gate_pre.shape != out.shape or \
+            (gate_bias is not None and gate_bias.shape[0] != out.shape[1]):
+        raise KernelError(f"gated_rows: delta {tuple(delta.shape)}, gate {tuple(gate_pre.shape)}, out {tuple(out.shape)}")
+    _check(_core(act).ib_gated_rows(_p(delta), _p(gate_pre), _p(gate_bias), _p(out), out.shape[0], out.shape[1],
+                                    _stream()), "gated_rows")
+
+
+def bias_add(x: torch.Tensor, bias: torch.Tensor):
+    """x[r, j] += bias[j] in place for the first len(bias) columns of every row; ``x`` in the activation dtype (a view
+    with unit last stride), ``bias`` float32."""
+    _need(bias, "bias", (torch.float32,), 1)
+    if not (x.is_cuda and x.dim() == 2 and x.dtype in _W and x.stride(1) == 1 and bias.shape[0] <= x.shape[1]):
+        raise KernelError(f"bias_add: x {tuple(x.shape)} {x.dtype}, bias {tuple(bias.shape)}")
+    _check(_core(x.dtype).ib_bias_add(x.data_ptr(), x.stride(0), _p(bias), x.shape[0], bias.shape[0], _stream()),
+           "bias_add")
+
+
+def scaled_sum(x: torch.Tensor, a: float, y: torch.Tensor, b: float, out: torch.Tensor):
+    """out = a * x + b * y, element by element in float32, stored in the activation dtype."""
+    act = out.dtype
+    _need(x, "x", (act,))
+    _need(y, "y", (act,))
+    _need(out, "out", _W)
+    if x.shape != out.shape or y.shape != out.shape:
+        raise KernelError(f"scaled_sum: x {tuple(x.shape)}, y {tuple(y.shape)}, out {tuple(out.shape)}")
+    _check(_core(act).ib_scaled_sum(_p(x), float(a), _p(y), float(b), _p(out), out.numel(), _stream()), "scaled_sum")
+
+
+def mix_queries(q: torch.Tensor, mix: torch.Tensor, n_kv_heads: int, out: torch.Tensor):
+    """out[r, h, c*D:(c+1)*D] = sum over the heads g of key/value group c of mix[h, g] * q[r, g, :]: queries whose
+    scores against all of a token's key heads, side by side, are the heads' own scores mixed by ``mix`` [H, H]."""
+    act = out.dtype
+    _need(q, "q", (act,), 3)
+    _need(mix, "mix", (torch.float32,), 2)
+    _need(out, "out", _W, 3)
+    n, heads, d = q.shape
+    if mix.shape != (heads, heads) or n_kv_heads <= 0 or heads % n_kv_heads or out.shape != (n, heads, n_kv_heads * d):
+        raise KernelError(f"mix_queries: q {tuple(q.shape)}, mix {tuple(mix.shape)}, out {tuple(out.shape)}")
+    _check(_core(act).ib_mix_queries(_p(q), _p(mix), _p(out), n, heads, int(n_kv_heads), d, _stream()), "mix_queries")
 
 
 ARGMAX_CHUNK = 8192      # vocabulary entries per block of the two-stage argmax
@@ -1369,6 +1516,15 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         tile_req, tile_row0, n_tiles = ctx.attention_tiles(MMA_KEYS // (nh // nkv))
         paged_attention_mma(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
                             ctx.positions, scale, window, out, False)
+
+
+def joint_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                    ctx, scale: float, window: Optional[int], dist_bias: Optional[torch.Tensor], out: torch.Tensor):
+    """Attention of every row of the step with joint queries (see :func:`mix_queries`): head h's score against a token
+    is its product with all of the token's key heads side by side, times ``scale``, minus dist_bias[h, distance];
+    values are those of the head's own group.  Picks the kernel for the sizes."""
+    paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out,
+                            joint=True, dist_bias=dist_bias)
 
 
 def penalties(logits: torch.Tensor, prev: torch.Tensor, n_prev: torch.Tensor, repetition: torch.Tensor,

@@ -2,3 +2,4 @@
 from . import qwen3  # noqa: F401
 from . import vebonex  # noqa: F401
 from . import tikizen  # noqa: F401
+from . import sefalorn  # noqa: F401

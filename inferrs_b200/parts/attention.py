@@ -41,6 +41,19 @@ class Attention:
             d.append(TensorDecl(spec.q_norm.weight, (spec.head_dim,), init="norm"))
         if spec.k_norm is not None and spec.k_norm.weight is not None and spec.own_kv:
             d.append(TensorDecl(spec.k_norm.weight, (spec.head_dim,), init="norm"))
+        if spec.q_bias is not None:
+            d.append(TensorDecl(spec.q_bias, (spec.n_heads * spec.head_dim,), init="uniform:0:0.1"))
+        if spec.own_kv and spec.k_bias is not None:
+            d.append(TensorDecl(spec.k_bias, (spec.n_kv_heads * spec.head_dim,), init="uniform:0:0.1"))
+        if spec.own_kv and spec.v_bias is not None:
+            d.append(TensorDecl(spec.v_bias, (spec.n_kv_heads * dv,), init="uniform:0:0.1"))
+        if spec.o_bias is not None:
+            d.append(TensorDecl(spec.o_bias, (spec.width,), init="uniform:0:0.1"))
+        if spec.distance_bias is not None:
+            d += [TensorDecl(spec.distance_bias[0], (spec.n_heads,), init="uniform:0.5:0.4"),
+                  TensorDecl(spec.distance_bias[1], (spec.n_heads,), init="uniform:0.5:0.4")]
+        if spec.head_mix is not None:
+            d.append(TensorDecl(spec.head_mix, (spec.n_heads, spec.n_heads), init="identity:0.2"))
         return d
 
     @staticmethod
@@ -75,8 +88,30 @@ class Attention:
         mats = [weights[spec.q_proj]]
         if spec.own_kv:
             mats += [weights[spec.k_proj], weights[spec.v_proj]]
-        self.qkv = Linear(fuse_rows(mats), rt)
-        self.o = Linear(weights[spec.o_proj], rt)
+        self.qkv = Linear(fuse_rows(mats), rt, bias=self._fused_bias(spec, weights, rt))
+        self.o = Linear(weights[spec.o_proj], rt, bias=None if spec.o_bias is None else weights[spec.o_bias])
+        # scores penalised by distance and mixed across heads: the mixing is linear, so it is done on the queries
+        # (one vector per key/value head and query head, see kernels.mix_queries), and the penalty, mixed the same
+        # way, is a table [heads, distances] that the attention kernel takes off the scores
+        self.talking = spec.distance_bias is not None or spec.head_mix is not None
+        if self.talking:
+            if not spec.own_kv:
+                raise ValueError("attention with mixed heads or a distance penalty keeps its own keys and values")
+            h = spec.n_heads
+            mix = weights[spec.head_mix].to(torch.float64) if spec.head_mix is not None \
+                else torch.eye(h, dtype=torch.float64, device=rt.device)
+            self.mix = mix.to(torch.float32).contiguous()
+            self.dist_bias = None
+            if spec.distance_bias is not None:
+                reach = spec.window or spec.position.max_positions
+                if not reach or reach <= 0:
+                    raise ValueError("a distance penalty needs a window or the model's number of positions "
+                                     "(position.max_positions)")
+                r1 = weights[spec.distance_bias[0]].to(torch.float64)
+                r2 = weights[spec.distance_bias[1]].to(torch.float64)
+                dist = torch.arange(reach, dtype=torch.float64, device=rt.device)
+                own = r1[:, None] * torch.log1p(r2[:, None] * dist[None, :])           # [heads, distances]
+                self.dist_bias = (mix @ own).to(torch.float32).contiguous()
         self.q_weight = weights[spec.q_norm.weight] if spec.q_norm is not None and spec.q_norm.weight else None
         self.k_weight = weights[spec.k_norm.weight] \
             if (spec.k_norm is not None and spec.k_norm.weight and spec.own_kv) else None
@@ -88,6 +123,19 @@ class Attention:
         self.interleaved = bool(getattr(position, "interleaved", False))   # which elements of a head turn together
         if self.rot_dim > spec.head_dim:
             raise ValueError(f"rot_dim {self.rot_dim} exceeds head_dim {spec.head_dim}")
+
+    @staticmethod
+    def _fused_bias(spec: AttentionSpec, weights, rt: Runtime):
+        """The biases of q, k and v side by side as the fused projection's columns lie (zeros where one is absent);
+        None if there is none at all."""
+        names = [spec.q_bias] + ([spec.k_bias, spec.v_bias] if spec.own_kv else [])
+        if all(n is None for n in names):
+            return None
+        dv = spec.value_dim or spec.head_dim
+        sizes = [spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim, spec.n_kv_heads * dv]
+        return torch.cat([weights[n].to(torch.float32) if n is not None
+                          else torch.zeros(size, dtype=torch.float32, device=rt.device)
+                          for n, size in zip(names, sizes)])
 
     # A block may hand this part scaled rows instead of a norm's output, and a sink instead of taking its result, where
     # both of its products fold norms at the step's number of rows (see SequentialBlock).
@@ -110,7 +158,12 @@ class Attention:
                                    norm_q=s.q_norm is not None, norm_k=s.k_norm is not None and s.own_kv,
                                    norm_after_rotation=s.norm_after_rotation)
         out = torch.empty((n, s.n_heads * self.value_dim), dtype=self.rt.dtype, device=h.device)
-        kernels.paged_attention(q, k_pages, v_pages, table, ctx, s.scale, self.span, out)
+        if self.talking:
+            mixed = torch.empty((n, s.n_heads, s.n_kv_heads * s.head_dim), dtype=self.rt.dtype, device=h.device)
+            kernels.mix_queries(q, self.mix, s.n_kv_heads, mixed)
+            kernels.joint_attention(mixed, k_pages, v_pages, table, ctx, s.scale, self.span, self.dist_bias, out)
+        else:
+            kernels.paged_attention(q, k_pages, v_pages, table, ctx, s.scale, self.span, out)
         return self.o(out, sink=sink)
 
 

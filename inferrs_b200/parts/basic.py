@@ -14,8 +14,25 @@ from .spec import NormSpec, PositionSpec, TensorDecl
 
 def _nothing_pending(delta):
     """A block that norms after the sum hands on a copy of the stream instead of an output that is still to be
-    added (an object with ``rows`` and no ``delta``): for a norm that means that nothing is pending."""
+    added (an object with ``rows`` and no ``delta``): for a norm that means that nothing is pending.  A gated
+    output (:class:`GatedUpdate`) becomes plain rows here, for the norms that do not apply the gate themselves."""
+    if isinstance(delta, GatedUpdate):
+        return delta.rows()
     return None if (delta is not None and hasattr(delta, "rows") and not hasattr(delta, "delta")) else delta
+
+
+class GatedUpdate:
+    """A sub-layer's output that has not been added to the residual stream yet and is to be multiplied by
+    sigmoid(gate_pre + gate_bias) on the way: the norm kernel that follows does gate, addition and norm in one pass
+    (:class:`LayerNorm`); any other norm asks for the gated rows (:meth:`rows`)."""
+
+    def __init__(self, delta: torch.Tensor, gate_pre: torch.Tensor, gate_bias: Optional[torch.Tensor]):
+        self.delta, self.gate_pre, self.gate_bias = delta, gate_pre, gate_bias
+
+    def rows(self) -> torch.Tensor:
+        out = torch.empty_like(self.delta)
+        kernels.gated_rows(self.delta, self.gate_pre, self.gate_bias, out)
+        return out
 
 
 class StreamUpdate:
@@ -85,6 +102,43 @@ class RMSNorm:
         return out
 
 
+class LayerNorm:
+    """(x - mean) / sqrt(variance + eps) * w in float32, the variance being the mean of the squared deviations; no
+    bias.  Fused with the residual addition that precedes it in a block, and with the gate on that addition where the
+    block before hands on a :class:`GatedUpdate`."""
+
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec: NormSpec) -> List[TensorDecl]:
+        return [TensorDecl(spec.weight, (spec.size,), init="norm")]
+
+    def __init__(self, spec: NormSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        if spec.weight is None or getattr(spec, "groups", 1) != 1:
+            raise ValueError("a layer norm of the residual stream has a weight and no groups")
+        self.spec = spec
+        self.rt = rt
+        self.weight = weights[spec.weight].to(torch.float32).contiguous()
+
+    def add_norm(self, residual: torch.Tensor, delta, rows: Optional[torch.Tensor] = None):
+        if residual.dim() != 2:
+            raise ValueError("a layer norm runs on the plain residual [rows, width]")
+        gate_pre = gate_bias = None
+        if isinstance(delta, GatedUpdate):
+            delta, gate_pre, gate_bias = delta.delta, delta.gate_pre, delta.gate_bias
+        else:
+            delta = _nothing_pending(delta)
+            if isinstance(delta, (StreamUpdate, kernels.ScaledRows)):
+                raise ValueError("a layer norm takes plain or gated rows from the block before it")
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.spec.size), dtype=self.rt.dtype, device=residual.device)
+        kernels.gated_add_layer_norm(residual, delta, gate_pre, gate_bias, self.weight, self.spec.eps, out, rows)
+        return out
+
+    def norm(self, x: torch.Tensor) -> torch.Tensor:
+        raise ValueError("a layer norm has no form that stands after a sub-layer")
+
+
 class NoNorm:
     """No norm: the sub-layer reads (or hands on) the rows as they are.  Still the place where the output of
     the sub-layer before it is added to the residual stream."""
@@ -111,6 +165,7 @@ class NoNorm:
 
 
 register_norm("rms", RMSNorm)
+register_norm("layer_norm", LayerNorm)
 register_norm("none", NoNorm)
 
 
@@ -211,27 +266,34 @@ def fuse_rows(tensors: Sequence[torch.Tensor]) -> torch.Tensor:
 
 
 class Linear:
-    """y = x W^T, W stored [out, in], no bias (candle-nn/src/linear.rs:41-82).
+    """y = x W^T (+ bias), W stored [out, in] (candle-nn/src/linear.rs:41-82).
 
     float32 runs: FFMA kernel.  bfloat16 runs: tensor-core product with float32 accumulation for a
     bfloat16 weight; a weight that is stored in float32 keeps its precision and goes through the
     FFMA kernel with the bfloat16 activations widened on the fly.
     """
 
-    def __init__(self, weight: torch.Tensor, rt: Runtime):
+    def __init__(self, weight: torch.Tensor, rt: Runtime, bias: Optional[torch.Tensor] = None):
+        """``bias`` [out] (or shorter: it is added to the first columns) is kept in float32 and added by a kernel of
+        its own after the product; a product with a bias folds no norms."""
         if weight.dim() != 2:
             raise ValueError(f"a linear weight must be a matrix, got shape {tuple(weight.shape)}")
         self.weight = weight.contiguous()
         self.rt = rt
         self.n_out, self.n_in = weight.shape
+        if bias is not None and (bias.dim() != 1 or bias.shape[0] > self.n_out):
+            raise ValueError(f"a bias of shape {tuple(bias.shape)} does not fit {self.n_out} outputs")
+        self.bias = None if bias is None else bias.to(torch.float32).contiguous()
 
     def __call__(self, x, out_dtype: Optional[torch.dtype] = None, sink=None):
         """``x`` may be :class:`~inferrs_b200.kernels.ScaledRows`; with a ``sink`` the result is added to the residual
         stream there and the next norm's scaled rows come back instead of the result."""
         out = torch.empty((x.shape[0], self.n_out), dtype=out_dtype or self.rt.dtype, device=x.device)
         scaled = kernels.linear(x, self.weight, out, self.rt.dtype, sink=sink)
+        if self.bias is not None:
+            kernels.bias_add(out, self.bias)
         return out if sink is None else scaled
 
     def folds_norms(self, n_rows: int) -> bool:
         """Whether this product takes scaled rows and feeds a sink at this number of rows."""
-        return kernels.folded_norm_supported(n_rows, self.rt.dtype, self.weight)
+        return self.bias is None and kernels.folded_norm_supported(n_rows, self.rt.dtype, self.weight)

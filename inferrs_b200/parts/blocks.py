@@ -6,7 +6,7 @@ from typing import List, Optional
 import torch
 
 from .. import kernels
-from .basic import StreamUpdate
+from .basic import GatedUpdate, Linear, StreamUpdate
 from .registry import register_arrangement
 from .spec import TensorDecl
 
@@ -204,3 +204,68 @@ def _no_norm():
 
 
 register_arrangement("norm_after_sum", NormAfterSumBlock)
+
+
+class GatedResidualBlock:
+    """For every sub-layer in turn: h = norm(x), x += sigmoid(W h + b) * part(h), with W and b from the sub-layer's
+    :class:`~inferrs_b200.parts.spec.ResidualGateSpec`.  The gate reads the same normalised rows as the part.
+
+    As in :class:`SequentialBlock` nothing is added where the sub-layer ends: the block hands its last sub-layer's
+    output on with the gate's pre-activations as a pending :class:`~inferrs_b200.parts.basic.GatedUpdate`, and the norm
+    kernel that follows does sigmoid, product, addition to the float32 stream and norm in one pass.
+    """
+
+    needs_weights = True     # the model hands the arrangement the weights too: the gates' tensors
+
+    @staticmethod
+    def declare(spec) -> List[TensorDecl]:
+        out = []
+        for s in spec.sublayers:
+            c = s.connection
+            if c is None or not hasattr(c, "weight") or not hasattr(c, "bias"):
+                raise ValueError("every sub-layer of a gated-residual block needs a residual gate")
+            width = _width_of(s)
+            out += [TensorDecl(c.weight, (width, width)), TensorDecl(c.bias, (width,), init="uniform:0:0.5")]
+        return out
+
+    def __init__(self, spec, sublayers: List[BuiltSubLayer], weights=None, rt=None):
+        if not sublayers:
+            raise ValueError("a layer needs at least one sub-layer")
+        if weights is None or rt is None:
+            raise ValueError("a gated-residual block needs the weights of its gates")
+        self.spec = spec
+        self.sublayers = list(sublayers)
+        self.gates = []
+        for s, built in zip(spec.sublayers, sublayers):
+            if s.connection is None or built.post_norm is not None or built.part is None \
+                    or not hasattr(built.norm, "add_norm"):
+                raise ValueError("a sub-layer of a gated-residual block has a part, a gate, a norm before it and none "
+                                 "after it")
+            self.gates.append((Linear(weights[s.connection.weight], rt),
+                               weights[s.connection.bias].to(torch.float32).contiguous()))
+
+    def parts(self):
+        for s in self.sublayers:
+            yield s.part
+            yield s.norm
+
+    def forward(self, ctx, cache_id: int, residual: torch.Tensor, pending):
+        if residual.dim() != 2:
+            raise ValueError("a gated-residual block runs on the plain residual [rows, width]")
+        for s, (gate, bias) in zip(self.sublayers, self.gates):
+            h = s.norm.add_norm(residual, pending)
+            y = s.run(ctx, cache_id, h)
+            pending = GatedUpdate(y, gate(h), bias)
+        return pending
+
+
+def _width_of(sub) -> int:
+    """The stream's width as a sub-layer's descriptions give it."""
+    for d in (sub.norm, sub.part):
+        for name in ("size", "width"):
+            if d is not None and hasattr(d, name):
+                return int(getattr(d, name))
+    raise ValueError("a sub-layer of a gated-residual block needs a norm or a part that says how wide the stream is")
+
+
+register_arrangement("gated_residual", GatedResidualBlock)

@@ -93,6 +93,10 @@ class RoutedExperts:
             raise ValueError(f"routed experts: {spec.top} of {n} experts cannot be chosen")
         if spec.shared is not None and spec.shared_inner <= 0:
             raise ValueError("routed experts: a shared expert needs its inner size")
+        modes = {"softmax_of_chosen": kernels.ROUTE_SOFTMAX_OF_CHOSEN, "sigmoid_share": kernels.ROUTE_SIGMOID_SHARE}
+        if spec.scoring not in modes:
+            raise ValueError(f"routed experts: no router scores by '{spec.scoring}'; known: {sorted(modes)}")
+        self.mode = modes[spec.scoring]
         self.spec, self.rt = spec, rt
         self.n_experts = n
         self.has_shared = spec.shared is not None
@@ -118,7 +122,7 @@ class RoutedExperts:
         logits = self.router(h, out_dtype=torch.float32)
         share = torch.empty((n, self.n_experts + int(self.has_shared)), dtype=torch.float32, device=h.device)
         kernels.router_topk(logits, self.router_bias, self.n_experts, self.spec.top, self.has_shared, share,
-                            self.rt.dtype)
+                            self.rt.dtype, mode=self.mode, scale=self.spec.route_scale)
         a = torch.empty((n, self.total_inner), dtype=self.rt.dtype, device=h.device)
         kernels.routed_gate(self.gate_up(h), share, self.n_experts, self.spec.inner, a)
         return self.down(a)

@@ -17,7 +17,8 @@ from ..cache.storage import StateNeed
 from ..runtime import Runtime
 from .basic import Linear, build_position, fuse_rows
 from .registry import register_mixer
-from .spec import ChannelDecayScanSpec, FixedDecayScanSpec, ScalarGateScanSpec, StateSpaceScanSpec, TensorDecl
+from .spec import (ChannelDecayScanSpec, FixedDecayScanSpec, GatedDeltaScanSpec, ScalarGateScanSpec,
+                   StateSpaceScanSpec, TensorDecl)
 
 
 class _ScanMixer:
@@ -123,16 +124,21 @@ class ScalarGateScan(_ScanMixer):
 class FixedDecayScan:
     """Retention (see :class:`~inferrs_b200.parts.spec.FixedDecayScanSpec`).  One product gives q, k, v and the gate;
     q and k are rotated (k also scaled) into float32 rows, the scan with one constant decay per head runs on those,
-    and the per-head division by the root mean square with the silu gate is one kernel before the output product."""
+    and the per-head division by the root mean square with the silu gate is one kernel before the output product.
+    The description's options (silu on q, k and v as they leave the projection, one root mean square over all heads,
+    a weight on the normed heads, a sigmoid gate, another factor on k) are flags of the same three kernels."""
 
     graph_safe = True
 
     @staticmethod
     def declare(spec: FixedDecayScanSpec) -> List[TensorDecl]:
         hd, he = spec.n_heads * spec.key_dim, spec.n_heads * spec.value_dim
-        return [TensorDecl(spec.q_proj, (hd, spec.width)), TensorDecl(spec.k_proj, (hd, spec.width)),
-                TensorDecl(spec.v_proj, (he, spec.width)), TensorDecl(spec.gate_proj, (he, spec.width)),
-                TensorDecl(spec.o_proj, (spec.width, he))]
+        d = [TensorDecl(spec.q_proj, (hd, spec.width)), TensorDecl(spec.k_proj, (hd, spec.width)),
+             TensorDecl(spec.v_proj, (he, spec.width)), TensorDecl(spec.gate_proj, (he, spec.width)),
+             TensorDecl(spec.o_proj, (spec.width, he))]
+        if spec.out_norm is not None:
+            d.append(TensorDecl(spec.out_norm, (he,), init="norm"))
+        return d
 
     @staticmethod
     def cache_need(spec):
@@ -156,10 +162,20 @@ class FixedDecayScan:
         self.cos, self.sin, self.rot_dim = build_position(spec.position, rt).tables()
         if self.rot_dim > spec.key_dim:
             raise ValueError(f"rot_dim {self.rot_dim} exceeds the key size {spec.key_dim}")
+        if spec.input_activation not in (None, "silu") or spec.gate_activation not in ("silu", "sigmoid"):
+            raise ValueError(f"a fixed-decay scan has no kernel for the activations '{spec.input_activation}' (inputs) "
+                             f"and '{spec.gate_activation}' (gate)")
+        act = spec.input_activation == "silu"
+        if act and self.rot_dim:
+            raise ValueError("a fixed-decay scan rotates its queries and keys or sends them through silu, not both")
+        key_scale = float(spec.key_dim) ** -0.5 if spec.key_scale is None else float(spec.key_scale)
+        turn = 0 if act else 1
         # q, k and v of a row as float32, side by side
-        self.slices = ((0, 0, spec.n_heads, spec.key_dim, 1, 1.0),
-                       (hd, hd, spec.n_heads, spec.key_dim, 1, float(spec.key_dim) ** -0.5),
-                       (2 * hd, 2 * hd, spec.n_heads, spec.value_dim, 0, 1.0))
+        self.slices = ((0, 0, spec.n_heads, spec.key_dim, turn, 1.0, act),
+                       (hd, hd, spec.n_heads, spec.key_dim, turn, key_scale, act),
+                       (2 * hd, 2 * hd, spec.n_heads, spec.value_dim, 0, 1.0, act))
+        self.out_norm = None if spec.out_norm is None else weights[spec.out_norm]
+        self.gate_act = kernels.GATE_SILU if spec.gate_activation == "silu" else kernels.GATE_SIGMOID
 
     def forward(self, ctx, cache_id: int, h):
         s = self.spec
@@ -172,7 +188,87 @@ class FixedDecayScan:
         kernels.decay_scan(x, 0, hd, 2 * hd, s.n_heads, self.decay, None, None, ctx.storage.state(cache_id), ctx.q_start,
                            ctx.slots, ctx.n_requests, o, s.key_dim, self.rt.dtype, max_rows=ctx.max_q_len)
         gated = torch.empty((n, he), dtype=self.rt.dtype, device=h.device)
-        kernels.head_norm_gate(o, proj[:, self.gate_col:], None, True, kernels.GATE_SILU, s.eps, gated)
+        if s.norm_heads_together:        # one root mean square over the heads side by side: one head as wide as all
+            o = o.view(n, 1, he)
+        kernels.head_norm_gate(o, proj[:, self.gate_col:], self.out_norm, True, self.gate_act, s.eps, gated)
+        return self.o(gated)
+
+
+class GatedDeltaScan:
+    """The gated delta rule (see :class:`~inferrs_b200.parts.spec.GatedDeltaScanSpec`).  One product gives the gate,
+    q, k, v and the two per-head numbers behind beta and the fade; one kernel does the short convolutions with silu
+    (reading what the state keeps of earlier steps) and turns the two numbers into beta and fade in float32; the scan
+    makes q and k unit vectors as it fetches them and runs the rule in float32; norm per head, weight and silu gate
+    are one kernel before the output product.  The state of a slot is the matrices [H, key_dim, value_dim] and then
+    the convolutions' last taps - 1 inputs [taps - 1, channels], float32."""
+
+    graph_safe = True
+
+    @staticmethod
+    def _sizes(spec: GatedDeltaScanSpec):
+        gd, he = spec.n_kv_heads * spec.key_dim, spec.n_heads * spec.value_dim
+        return gd, he, 2 * gd + he           # q or k columns, v or gate columns, the convolutions' channels
+
+    @staticmethod
+    def declare(spec: GatedDeltaScanSpec) -> List[TensorDecl]:
+        gd, he, _ = GatedDeltaScan._sizes(spec)
+        return [TensorDecl(spec.q_proj, (gd, spec.width)), TensorDecl(spec.k_proj, (gd, spec.width)),
+                TensorDecl(spec.v_proj, (he, spec.width)),
+                TensorDecl(spec.q_conv, (gd, spec.taps), init="uniform:0:0.5"),
+                TensorDecl(spec.k_conv, (gd, spec.taps), init="uniform:0:0.5"),
+                TensorDecl(spec.v_conv, (he, spec.taps), init="uniform:0:0.5"),
+                TensorDecl(spec.beta_proj, (spec.n_heads, spec.width)),
+                TensorDecl(spec.a_proj, (spec.n_heads, spec.width)),
+                TensorDecl(spec.a_log, (spec.n_heads,), init="uniform:0:1"),
+                TensorDecl(spec.dt_bias, (spec.n_heads,), init="uniform:-2:1"),
+                TensorDecl(spec.gate_proj, (he, spec.width)),
+                TensorDecl(spec.out_norm, (spec.value_dim,), init="norm"),
+                TensorDecl(spec.o_proj, (spec.width, he))]
+
+    @staticmethod
+    def cache_need(spec):
+        return None
+
+    @staticmethod
+    def state_need(spec: GatedDeltaScanSpec) -> Optional[StateNeed]:
+        _, _, channels = GatedDeltaScan._sizes(spec)
+        return StateNeed(shape=(spec.n_heads * spec.key_dim * spec.value_dim + (spec.taps - 1) * channels,))
+
+    def __init__(self, spec: GatedDeltaScanSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        if spec.n_heads % spec.n_kv_heads or spec.taps < 1 or spec.unit_eps < 0:
+            raise ValueError(f"a gated delta rule needs heads that divide into its key heads, at least one tap and a "
+                             f"unit_eps that is not negative, got {spec}")
+        self.spec, self.rt = spec, rt
+        self.gd, self.he, self.channels = self._sizes(spec)
+        # columns of a projected row: gate | q | k | v | a | beta
+        self.in_proj = Linear(fuse_rows([weights[spec.gate_proj], weights[spec.q_proj], weights[spec.k_proj],
+                                         weights[spec.v_proj], weights[spec.a_proj], weights[spec.beta_proj]]), rt)
+        self.o = Linear(weights[spec.o_proj], rt)
+        f32 = lambda name: weights[name].to(torch.float32).contiguous()     # noqa: E731
+        self.conv = torch.cat([f32(spec.q_conv), f32(spec.k_conv), f32(spec.v_conv)], dim=0).contiguous()
+        self.dt_bias, self.a_log = f32(spec.dt_bias), f32(spec.a_log)
+        self.out_norm = weights[spec.out_norm]
+        self.conv_state_off = spec.n_heads * spec.key_dim * spec.value_dim
+        self.a_col = self.he + self.channels
+
+    def forward(self, ctx, cache_id: int, h):
+        s = self.spec
+        n = h.shape[0]
+        proj = self.in_proj(h)
+        state = ctx.storage.state(cache_id)
+        qkv = torch.empty((n, self.channels), dtype=torch.float32, device=h.device)
+        gates = torch.empty((n, 2 * s.n_heads), dtype=torch.float32, device=h.device)      # fade | beta
+        kernels.conv_silu_gates(proj, self.he, self.conv, None, state, self.conv_state_off, ctx.q_start, ctx.slots,
+                                ctx.row_request, qkv, self.a_col, self.dt_bias, self.a_log, gates,
+                                beta_col=self.a_col + s.n_heads)
+        kernels.conv_state_shift(proj, self.he, self.channels, s.taps, state, self.conv_state_off, ctx.q_start,
+                                 ctx.slots, ctx.n_requests)
+        o = torch.empty((n, s.n_heads, s.value_dim), dtype=torch.float32, device=h.device)
+        kernels.delta_scan(qkv, 0, self.gd, 2 * self.gd, s.n_kv_heads, gates[:, :s.n_heads], gates[:, s.n_heads:],
+                           s.unit_eps, float(s.key_dim) ** -0.5, state, ctx.q_start, ctx.slots, ctx.n_requests, o,
+                           s.key_dim, self.rt.dtype, max_rows=ctx.max_q_len)
+        gated = torch.empty((n, self.he), dtype=self.rt.dtype, device=h.device)
+        kernels.head_norm_gate(o, proj[:, :self.he], self.out_norm, True, kernels.GATE_SILU, s.eps, gated)
         return self.o(gated)
 
 
@@ -250,4 +346,5 @@ class StateSpaceScan:
 register_mixer("channel_decay_scan", ChannelDecayScan)
 register_mixer("fixed_decay_scan", FixedDecayScan)
 register_mixer("state_space_scan", StateSpaceScan)
+register_mixer("gated_delta_scan", GatedDeltaScan)
 register_mixer("scalar_gate_scan", ScalarGateScan)

@@ -35,7 +35,8 @@ class TensorDecl:
 class NormSpec:
     """x / sqrt(mean(x^2) + eps) * weight.  ``groups`` > 1: the row is cut into that many equal consecutive parts
     and each part is divided by its own root mean square.  ``weight`` None (where a part allows it: the per-head
-    norms of attention): the division alone."""
+    norms of attention): the division alone.  ``kind="layer_norm"``: (x - mean) / sqrt(variance + eps) * weight, the
+    variance being the mean of the squared deviations from the mean; no bias."""
 
     size: int
     eps: float
@@ -74,6 +75,10 @@ class AttentionSpec:
     layer that has no key/value projections and reads the cache that another schedule
     entry writes.  ``value_dim``: the size of a value head where it differs from ``head_dim``.
     ``norm_after_rotation``: the per-head norms of queries and keys come after the rotation instead of before it.
+    ``q_bias`` / ``k_bias`` / ``v_bias`` / ``o_bias``: vectors added to the projections' results.
+    ``distance_bias`` = (r1, r2), two tensors [n_heads]: r1_h ln(1 + r2_h (i - j)) is taken off head h's scaled score
+    of query i against key j.  ``head_mix`` [n_heads, n_heads]: after that the heads' scores are mixed,
+    score_h <- sum_g mix[h, g] score_g, before mask and softmax (every head still reads the values of its own group).
     """
 
     width: int
@@ -94,6 +99,12 @@ class AttentionSpec:
     value_dim: Optional[int] = None
     chunk: Optional[int] = None
     norm_after_rotation: bool = False
+    q_bias: Optional[str] = None
+    k_bias: Optional[str] = None
+    v_bias: Optional[str] = None
+    o_bias: Optional[str] = None
+    distance_bias: Optional[Tuple[str, str]] = None
+    head_mix: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -118,7 +129,9 @@ class RoutedExpertsSpec:
     experts with the largest logits are chosen and weighed by the softmax over the chosen logits alone; the output is
     the weighted sum of down_e( silu(gate_e(x)) * up_e(x) ) over the chosen.  ``experts`` names every expert's
     (gate, up, down) tensors.  ``shared`` (optional, (gate, up, down, gate vector) with ``shared_inner``): an expert
-    that every token uses; its output is added times sigmoid(gate_vector . x)."""
+    that every token uses; its output is added times sigmoid(gate_vector . x).
+    ``scoring="sigmoid_share"``: the scores are s = sigmoid(z), the ``top`` largest scores are chosen, and a chosen
+    expert weighs s_e / (sum of the chosen scores + 1e-20).  ``route_scale`` multiplies the routed experts' weights."""
 
     width: int
     inner: int
@@ -129,14 +142,19 @@ class RoutedExpertsSpec:
     shared: Optional[Tuple[str, str, str, str]] = None
     shared_inner: int = 0
     kind: str = "routed_experts"
+    scoring: str = "softmax_of_chosen"
+    route_scale: float = 1.0
 
 
 @dataclass(frozen=True)
 class FixedDecayScanSpec:
     """Retention: linear attention whose state fades by a fixed factor per head; the scores go through no softmax and no normaliser.  Per head a
     matrix state S [key_dim, value_dim], S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t; q and k are rotated by
-    position (``position``), k is then multiplied by key_dim^(-1/2); each head's o is divided by its root mean square
-    (no weight); the heads times silu(gate(x)) go through ``o_proj``."""
+    position (``position``), k is then multiplied by key_dim^(-1/2) (``key_scale`` if given); each head's o is divided
+    by its root mean square (no weight); the heads times silu(gate(x)) go through ``o_proj``.
+    ``input_activation="silu"``: q, k and v go through silu as they leave their projections (such heads are not
+    rotated).  ``norm_heads_together``: the heads' o side by side are divided by one root mean square over all of
+    them.  ``out_norm`` [n_heads * value_dim]: a weight on the normed o.  ``gate_activation``: "silu" or "sigmoid"."""
 
     width: int
     n_heads: int
@@ -151,6 +169,61 @@ class FixedDecayScanSpec:
     gate_proj: str
     o_proj: str
     kind: str = "fixed_decay_scan"
+    input_activation: Optional[str] = None
+    key_scale: Optional[float] = None
+    norm_heads_together: bool = False
+    out_norm: Optional[str] = None
+    gate_activation: str = "silu"
+
+
+@dataclass(frozen=True)
+class GatedDeltaScanSpec:
+    """The gated delta rule.  q and k [n_kv_heads, key_dim] and v [n_heads, value_dim] leave their projections through
+    a causal convolution per channel over the last ``taps`` inputs (``*_conv`` [channels, taps], the last tap weighing
+    the token itself, no bias, zeros before the start) and silu; q and k are then made unit vectors per head,
+    x / sqrt(sum(x^2) + unit_eps), and q is multiplied by key_dim^(-1/2).  Per head (head h reads q/k head
+    h / (n_heads / n_kv_heads)) a state S [key_dim, value_dim] with beta = sigmoid(beta_proj(x)) and
+    fade = exp(-exp(a_log_h) softplus(a_proj(x) + dt_bias_h)):
+    S <- fade S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q (the read-out sees the token's own write).
+    Each head's o is divided by its root mean square (``eps``), multiplied by ``out_norm`` [value_dim] (one weight for
+    all heads) and by silu(gate(x)), and goes through ``o_proj``.  The convolutions' last taps - 1 inputs belong to
+    the per-request state."""
+
+    width: int
+    n_heads: int
+    n_kv_heads: int
+    key_dim: int
+    value_dim: int
+    taps: int
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    q_conv: str
+    k_conv: str
+    v_conv: str
+    beta_proj: str
+    a_proj: str
+    a_log: str
+    dt_bias: str
+    gate_proj: str
+    out_norm: str
+    o_proj: str
+    unit_eps: float = 1e-6
+    kind: str = "gated_delta_scan"
+
+
+@dataclass(frozen=True)
+class MixerSumSpec:
+    """Two mixers side by side on the same input: ``left_scale`` * left(x) + ``right_scale`` * right(x).  The layer's
+    schedule entry names one cache id; at most one of the two keeps pages of keys and values and at most one a
+    per-request state (one of each is fine: they share the id)."""
+
+    left: Any
+    right: Any
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    kind: str = "mixer_sum"
 
 
 @dataclass(frozen=True)
@@ -294,6 +367,15 @@ class StreamConnectionSpec:
 
 
 @dataclass(frozen=True)
+class ResidualGateSpec:
+    """A sub-layer's result is multiplied element by element by sigmoid(weight h + bias) before it joins the stream,
+    h being what the sub-layer itself reads (the norm's output).  ``weight`` [width, width], ``bias`` [width]."""
+
+    weight: str
+    bias: str
+
+
+@dataclass(frozen=True)
 class SubLayerSpec:
     """One sub-layer of a block: a part with what stands before and after it.
 
@@ -307,7 +389,8 @@ class SubLayerSpec:
     category: str
     norm: Optional[Any] = None
     post_norm: Optional[Any] = None
-    # for arrangements whose sub-layers hang on the residual in a way of their own (StreamConnectionSpec)
+    # for arrangements whose sub-layers hang on the residual in a way of their own (StreamConnectionSpec,
+    # ResidualGateSpec)
     connection: Optional[Any] = None
     # for the arrangement that norms after the sum: the norm of the stream itself once the part's output is in it
     sum_norm: Optional[Any] = None
@@ -324,6 +407,9 @@ class LayerSpec:
 
     ``arrangement="norm_after_sum"``: for every sub-layer in turn, x <- sum_norm(residual_scale * x + part(x)): the
     parts read the stream itself, and the stream itself is normalised (``part`` None: the sum is residual_scale * x).
+
+    ``arrangement="gated_residual"``: for every sub-layer in turn, h = norm(x), x += sigmoid(W h + b) * part(h), with
+    W and b from the sub-layer's ``connection`` (a :class:`ResidualGateSpec`).
     """
 
     sublayers: Tuple[SubLayerSpec, ...]
