@@ -17,7 +17,8 @@ mask {size}}, right {heads, kv_heads, dim, vdim, conv}, left_scale, right_scale)
 A key that the chosen part needs and that is absent is an error: no size stands in code.  Keys that this reader does
 not know inside `norm`, a layer, its mixer or its feed-forward are an error too, so that a variant of the design is
 refused instead of being run as this one; an unknown key at the top (a seed, a name) is named on standard error and
-ignored.
+ignored.  A layer without a feed-forward has no second norm and no second gate; where the weight files hold them all
+the same (``l<i>.norm2``), they are read and do nothing.
 """
 from __future__ import annotations
 
@@ -55,6 +56,7 @@ class SefalornLayer:
     type: str
     mixer: Tuple[Tuple[str, Any], ...]            # the mixer's sizes and constants, as sorted (key, value) pairs
     mlp: Optional[Tuple[Tuple[str, Any], ...]]    # the feed-forward's; None: the layer has none
+    idle_second: bool = False                     # no feed-forward, but its norm and gate are in the weight files
 
     def get(self, key: str, default=None):
         return _thaw(dict(self.mixer).get(key, default))
@@ -121,6 +123,19 @@ class SefalornConfig:
             raise ConfigError(f"{src}: eos_token_id must be token ids inside the vocabulary, got {eos!r}")
         return cls(vocab=vocab, width=width, max_positions=max_positions, norm_eps=eps, logit_scale=float(logit_scale),
                    layers=tuple(layers), eos_token_ids=eos_ids)
+
+    def with_tensor_shapes(self, shapes: Dict[str, Tuple[int, ...]]) -> "SefalornConfig":
+        """The configuration with what only the weight files say: whether a layer without a feed-forward still
+        brings a second norm and gate."""
+        return _with_tensor_shapes(self, shapes)
+
+
+def _with_tensor_shapes(cfg: "SefalornConfig", shapes: Dict[str, Tuple[int, ...]]) -> "SefalornConfig":
+    layers = list(cfg.layers)
+    for i, layer in enumerate(layers):
+        if layer.mlp is None and f"l{i}.norm2" in shapes:
+            layers[i] = SefalornLayer(type=layer.type, mixer=layer.mixer, mlp=None, idle_second=True)
+    return SefalornConfig(**{**cfg.__dict__, "layers": tuple(layers)})
 
 
 def _keys(src: str, where: str, given, need: set, optional: set = frozenset()) -> Dict[str, Any]:

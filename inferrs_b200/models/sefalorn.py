@@ -85,7 +85,7 @@ def build_spec(cfg: SefalornConfig) -> ModelSpec:
         subs = [SubLayerSpec(part=_mixer(cfg, i), category="mixer", norm=_norm(cfg, f"l{i}.norm1"),
                              connection=ResidualGateSpec(weight=f"l{i}.rg1", bias=f"l{i}.rg1.b"))]
         ff = _feed_forward(cfg, i)
-        if ff is not None:
+        if ff is not None or cfg.layers[i].idle_second:
             subs.append(SubLayerSpec(part=ff, category="feed_forward", norm=_norm(cfg, f"l{i}.norm2"),
                                      connection=ResidualGateSpec(weight=f"l{i}.rg2", bias=f"l{i}.rg2.b")))
         layers.append(LayerSpec(sublayers=tuple(subs), arrangement="gated_residual"))

@@ -208,7 +208,8 @@ register_arrangement("norm_after_sum", NormAfterSumBlock)
 
 class GatedResidualBlock:
     """For every sub-layer in turn: h = norm(x), x += sigmoid(W h + b) * part(h), with W and b from the sub-layer's
-    :class:`~inferrs_b200.parts.spec.ResidualGateSpec`.  The gate reads the same normalised rows as the part.
+    :class:`~inferrs_b200.parts.spec.ResidualGateSpec`.  The gate reads the same normalised rows as the part.  A
+    sub-layer without a part adds nothing: its norm's and gate's tensors are read and not used.
 
     As in :class:`SequentialBlock` nothing is added where the sub-layer ends: the block hands its last sub-layer's
     output on with the gate's pre-activations as a pending :class:`~inferrs_b200.parts.basic.GatedUpdate`, and the norm
@@ -237,22 +238,23 @@ class GatedResidualBlock:
         self.sublayers = list(sublayers)
         self.gates = []
         for s, built in zip(spec.sublayers, sublayers):
-            if s.connection is None or built.post_norm is not None or built.part is None \
-                    or not hasattr(built.norm, "add_norm"):
-                raise ValueError("a sub-layer of a gated-residual block has a part, a gate, a norm before it and none "
-                                 "after it")
+            if s.connection is None or built.post_norm is not None or not hasattr(built.norm, "add_norm"):
+                raise ValueError("a sub-layer of a gated-residual block has a gate, a norm before it and none after it")
             self.gates.append((Linear(weights[s.connection.weight], rt),
                                weights[s.connection.bias].to(torch.float32).contiguous()))
 
     def parts(self):
         for s in self.sublayers:
-            yield s.part
+            if s.part is not None:
+                yield s.part
             yield s.norm
 
     def forward(self, ctx, cache_id: int, residual: torch.Tensor, pending):
         if residual.dim() != 2:
             raise ValueError("a gated-residual block runs on the plain residual [rows, width]")
         for s, (gate, bias) in zip(self.sublayers, self.gates):
+            if s.part is None:
+                continue
             h = s.norm.add_norm(residual, pending)
             y = s.run(ctx, cache_id, h)
             pending = GatedUpdate(y, gate(h), bias)
