@@ -70,7 +70,9 @@ def window_attention(h, m: dict, w: Dict[str, torch.Tensor], p: str) -> torch.Te
     v = (h @ w[f"{p}.v"].T + w[f"{p}.v.b"]).view(T, G, E)
     pos = torch.arange(T)
     dist = (pos[:, None] - pos[None, :])
-    see = (dist >= 0) & (dist < int(m["mask"]["size"]))
+    see = dist >= 0
+    if m.get("mask"):                                   # no mask: every earlier position is seen
+        see = see & (dist < int(m["mask"]["size"]))
     far = dist.clamp(min=0).to(h.dtype)
     scores = torch.zeros(H, T, T, dtype=h.dtype)
     for head in range(H):
