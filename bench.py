@@ -27,6 +27,13 @@ does the same for the Tikizen design (attention in chunks, the state-space mixer
 layer's keys and values; a dense feed-forward and routed experts) beside the Vebonex design, the closest existing
 model (scans with a matrix state beside attention, per-request state slots beside pages), at equal width, heads,
 layers and feed-forward parameters, and its scan beside Vebonex's scans.
+
+    python bench.py --design sefalorn [--design-layers N]
+
+does the same for the Sefalorn design (window attention with mixed heads and a distance penalty beside the gated
+delta rule, lightning attention, gated residuals, routed experts) beside the Tikizen design, the closest existing
+model (attention over a bounded span, scans with a fixed decay, routed experts), and its scan and attention kernels
+each beside the like kernel at equal sizes.
 """
 from __future__ import annotations
 
@@ -224,6 +231,25 @@ def tikizen_config(width: int, heads: int, ff: int, n_layers: int, vocab: int) -
             "max_positions": 8192, "layers": [layer(i) for i in range(n_layers)]}
 
 
+def sefalorn_config(width: int, heads: int, ff: int, n_layers: int, vocab: int) -> dict:
+    """Layers in the order parallel (window attention of heads / 2 heads beside the gated delta rule of heads / 2
+    heads), lightning, repeated; eight routed experts of ff / 8 (two chosen) after every mixer."""
+    moe = {"kind": "moe", "expert": {"ff": ff // 8}, "router": {"experts": 8, "top": 2, "scale": 1.0}}
+
+    def layer(i):
+        if i % 2 == 0:
+            left = {"heads": heads // 2, "kv_heads": max(heads // 8, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                    "mask": {"size": 1024}}
+            right = {"heads": heads // 2, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4}
+            return {"type": "parallel", "mlp": moe,
+                    "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}}
+        return {"type": "lightning", "mlp": moe,
+                "mixer": {"heads": heads, "dim": 128, "vdim": 128,
+                          "decay": [1.0 - 2.0 ** (-5 - 3 * h / heads) for h in range(heads)]}}
+    return {"architecture": "Sefalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "max_positions": 8192, "layers": [layer(i) for i in range(n_layers)]}
+
+
 def design_bench(args) -> int:
     import argparse as ap_
     import gc
@@ -296,6 +322,44 @@ def design_bench(args) -> int:
         r["frac_bf16"] = round(r["TFLOPs"] / pk["bf16_tflops"], 4)
         return r
 
+    if args.design == "sefalorn":
+        sizes = []
+        for name, width, heads, ff in (("width 2048", 2048, 16, 8192), ("width 4096", 4096, 32, 16384)):
+            n_layers = args.design_layers
+            ours = measure(sefalorn_config(width, heads, ff, n_layers, vocab))
+            closest = measure(tikizen_config(width, heads, ff, n_layers, vocab))
+            sizes.append({"size": name, "layers": n_layers, "heads": heads, "ff": ff, "sefalorn": ours,
+                          "tikizen_equal_size": closest})
+        rows = []
+        for heads in (16, 32):
+            half = heads // 2
+            # the design's kernels, each followed by the like kernel of the closest model at equal sizes
+            rows.append(microbench.scan(ns(mode="delta", groups=0, form="prefill", batch=1, tokens=2048, heads=half,
+                                           key_dim=128, value_dim=128)))
+            rows.append(microbench.scan(ns(mode="scalar", groups=0, form="prefill", batch=1, tokens=2048, heads=half,
+                                           key_dim=128, value_dim=128)))
+            for b in (8, 64):
+                rows.append(microbench.scan(ns(mode="delta", groups=0, form="decode", batch=b, tokens=1, heads=half,
+                                               key_dim=128, value_dim=128)))
+                rows.append(microbench.scan(ns(mode="scalar", groups=0, form="decode", batch=b, tokens=1, heads=half,
+                                               key_dim=128, value_dim=128)))
+            kv = max(heads // 8, 1)
+            rows.append(microbench.joint(ns(form="prefill", impl="mma", batch=1, context=2048, tokens=2048, context_before=0,
+                                            window=1024, splits=0, heads=half, kv_heads=kv, head_dim=128)))
+            rows.append(microbench.attention(ns(form="prefill", impl="mma", batch=1, context=2048, tokens=2048,
+                                                context_before=0, splits=0, min_tiles=0, max_context=0, heads=half,
+                                                kv_heads=kv, head_dim=128)))
+            for b in (8, 64):
+                rows.append(microbench.joint(ns(form="decode", impl="mma", batch=b, context=2048, tokens=1, context_before=0,
+                                                window=1024, splits=0, heads=half, kv_heads=kv, head_dim=128)))
+                rows.append(microbench.attention(ns(form="decode", impl="mma", batch=b, context=1024, tokens=1,
+                                                    context_before=0, splits=0, min_tiles=0, max_context=0, heads=half,
+                                                    kv_heads=kv, head_dim=128)))
+        print(json.dumps({"design": "Sefalorn", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights",
+                          "prompt_len": PROMPT_LEN, "decode_batch": batch, "decode_steps": args.design_steps,
+                          "peaks": pk, "sizes": sizes, "kernels": [fractions(r) for r in rows]}))
+        return 0
+
     if args.design == "tikizen":
         sizes = []
         for name, width, heads, ff in (("width 2048", 2048, 16, 8192), ("width 4096", 4096, 32, 16384)):
@@ -362,7 +426,7 @@ def main() -> int:
     ap.add_argument("--clock-interval-ms", type=int, default=200, help="how often nvidia-smi is asked for the clocks")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points and the prefill")
     ap.add_argument("--no-workloads", action="store_true", help="skip the Qwen3-0.6B and Qwen3-32B workloads")
-    ap.add_argument("--design", choices=["vebonex", "tikizen"],
+    ap.add_argument("--design", choices=["vebonex", "tikizen", "sefalorn"],
                     help="another workload: this design beside the closest model")
     ap.add_argument("--design-layers", type=int, default=8, help="layers of both models of --design")
     ap.add_argument("--design-steps", type=int, default=64, help="timed decode steps of --design")

@@ -15,17 +15,23 @@
 //
 // Work split: S^T k needs a whole column of S for every token, so a column is not cut over warps: a warp owns 8
 // columns, and the 4 lanes that share a column own RL consecutive rows each (RL = 8, 16, 32 or 64 by D), in
-// registers; two shuffles add their shares of S^T k and two more those of S^T q.  A block holds 2 or 4 such warps
-// of one (request, head).  Tokens go in chunks of 16 through shared memory, two buffers: the next chunk's q, k, v,
-// fade and beta are on their way (cp.async) while the chunk before is walked; the factors that make q and k unit
-// vectors are one number per token, made once per chunk, and multiply the sums instead of the vectors.  A step of
-// single tokens takes chunks of one.
+// registers.  A block holds 2 or 4 such warps of one (request, head).  What a token costs is the chain from one
+// state to the next, so the chain is kept short: the read-out is taken from the state before the write,
+//     o_t = S_t^T q_t = fade_t (S_(t-1)^T q_t) + (k_t . q_t) u_t,
+// so that S_(t-1)^T k_t and S_(t-1)^T q_t are one pass over the registers with eight sums in flight and one pair of
+// shuffles for both; k_t . q_t and the factors that make q and k unit vectors are one number each per token, made
+// once per chunk, and multiply the sums instead of the vectors; the next token's q and k are fetched into registers
+// while this token's sums are made.  Tokens go in chunks of 16 through shared memory, two buffers: the next chunk's
+// q, k, v, fade and beta are on their way (cp.async) while the chunk before is walked.  In shared memory a lane's RL
+// rows of q and k are followed by four unused floats, so that the four lanes of a column read different banks.  A
+// step of single tokens takes chunks of one.
 //
 // State of one slot: S as [H, D, E] floats (E contiguous) from the slot's first float on.
 #include "common.cuh"
 
 #define GD_COLS 8      // columns of S per warp
 #define GD_PARTS 4     // lanes that share a column
+#define GD_PAD 4       // floats between two lanes' rows of q and k in shared memory
 
 __device__ __forceinline__ void gd_copy4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -43,7 +49,8 @@ __global__ void delta_scan_kernel(const float* __restrict__ x, long ld, int q_co
                                   float* __restrict__ out, int H, int D, int E) {
     extern __shared__ __align__(16) float smem[];
     ib_grid_dependency_sync();
-    constexpr int Dp = RL * GD_PARTS;                             // D rounded up: the rows beyond D hold zeros
+    constexpr int Dp = (RL + GD_PAD) * GD_PARTS;                  // a token's q or k in shared memory
+    constexpr bool AHEAD = RL <= 32 && CH > 1;                    // with 64 rows per lane a second pair does not fit
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int col = lane & (GD_COLS - 1), part = lane / GD_COLS;
     const int cols = n_warps * GD_COLS;                           // columns of the block
@@ -56,13 +63,15 @@ __global__ void delta_scan_kernel(const float* __restrict__ x, long ld, int q_co
     float* o_s = smem + 2 * buf_floats;                           // [CH][cols]
     float* qn_s = o_s + CH * cols;                                // [CH] what q's sums are multiplied by
     float* kn_s = qn_s + CH;                                      // [CH] what k's sums are multiplied by
-    // what no copy writes stays zero: the rows beyond D and the columns beyond E
+    float* kq_s = kn_s + CH;                                      // [CH] k . q as they were fetched
+    // what no copy writes stays zero: the rows beyond D, the floats between the lanes' rows, the columns beyond E
     for (int i = threadIdx.x; i < 2 * buf_floats; i += blockDim.x) smem[i] = 0.0f;
     __syncthreads();
+    auto place = [](int d) { return (d / RL) * (RL + GD_PAD) + (d % RL); };      // where row d of q or k lies
 
     float* st = state + (long)slots[r] * slot_stride + (long)h * D * E;
     const bool col_ok = e0 + ec < E;
-    const int dl = part * RL;
+    const int dl = part * RL, dl_s = part * (RL + GD_PAD);
     float S[RL];
 #pragma unroll
     for (int i = 0; i < RL; ++i) S[i] = (col_ok && dl + i < D) ? st[(long)(dl + i) * E + e0 + ec] : 0.0f;
@@ -79,8 +88,8 @@ __global__ void delta_scan_kernel(const float* __restrict__ x, long ld, int q_co
             for (int idx = threadIdx.x; idx < nc * d4; idx += blockDim.x) {
                 const int t = idx / d4, d = (idx - t * d4) << 2;
                 const float* xr = x + (long)(c0 + t) * ld + g * D + d;
-                gd_copy16(q_s + t * Dp + d, xr + q_col);
-                gd_copy16(k_s + t * Dp + d, xr + k_col);
+                gd_copy16(q_s + t * Dp + place(d), xr + q_col);
+                gd_copy16(k_s + t * Dp + place(d), xr + k_col);
             }
             const int e4 = e_n >> 2;
             for (int idx = threadIdx.x; idx < nc * e4; idx += blockDim.x) {
@@ -91,8 +100,8 @@ __global__ void delta_scan_kernel(const float* __restrict__ x, long ld, int q_co
             for (int idx = threadIdx.x; idx < nc * D; idx += blockDim.x) {
                 const int t = idx / D, d = idx - t * D;
                 const float* xr = x + (long)(c0 + t) * ld + g * D + d;
-                gd_copy4(q_s + t * Dp + d, xr + q_col);
-                gd_copy4(k_s + t * Dp + d, xr + k_col);
+                gd_copy4(q_s + t * Dp + place(d), xr + q_col);
+                gd_copy4(k_s + t * Dp + place(d), xr + k_col);
             }
             for (int idx = threadIdx.x; idx < nc * e_n; idx += blockDim.x) {
                 const int t = idx / e_n, e = idx - t * e_n;
@@ -121,58 +130,75 @@ __global__ void delta_scan_kernel(const float* __restrict__ x, long ld, int q_co
         const float* k_s = q_s + CH * Dp;
         const float* v_s = k_s + CH * Dp;
         const float* g_s = v_s + CH * cols;
-        // ---- one factor per token for q and for k (a warp per token) ------------------------------------------
+        // ---- three numbers per token: the unit factors of q and k, and k . q (a warp per token) ---------------
         for (int t = warp; t < nc; t += n_warps) {
-            float sq = 0.0f, sk = 0.0f;
-            if (unit_eps >= 0.0f) {
-                for (int d = lane; d < D; d += 32) {
-                    const float a = q_s[t * Dp + d], b = k_s[t * Dp + d];
-                    sq = fmaf(a, a, sq);
-                    sk = fmaf(b, b, sk);
-                }
-                sq = ib_warp_sum(sq);
-                sk = ib_warp_sum(sk);
+            float sq = 0.0f, sk = 0.0f, kq = 0.0f;
+            for (int d = lane; d < D; d += 32) {
+                const float a = q_s[t * Dp + place(d)], b = k_s[t * Dp + place(d)];
+                sq = fmaf(a, a, sq);
+                sk = fmaf(b, b, sk);
+                kq = fmaf(a, b, kq);
             }
+            sq = ib_warp_sum(sq);
+            sk = ib_warp_sum(sk);
+            kq = ib_warp_sum(kq);
             if (lane == 0) {
                 qn_s[t] = unit_eps >= 0.0f ? q_scale / sqrtf(sq + unit_eps) : q_scale;
                 kn_s[t] = unit_eps >= 0.0f ? 1.0f / sqrtf(sk + unit_eps) : 1.0f;
+                kq_s[t] = kq;
             }
         }
         __syncthreads();
         // ---- the tokens, one after the other ------------------------------------------------------------------
-        for (int t = 0; t < nc; ++t) {
-            const float fd = g_s[t], bt = g_s[CH + t], qn = qn_s[t], kn = kn_s[t];
-            const float vt = v_s[t * cols + ec];
-            const float4* k4 = reinterpret_cast<const float4*>(k_s + t * Dp + dl);
-            const float4* q4 = reinterpret_cast<const float4*>(q_s + t * Dp + dl);
-            float kr[RL];
-            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+        auto load = [&](float (&kd)[RL], float (&qd)[RL], int t) {
+            const float4* k4 = reinterpret_cast<const float4*>(k_s + t * Dp + dl_s);
+            const float4* q4 = reinterpret_cast<const float4*>(q_s + t * Dp + dl_s);
 #pragma unroll
             for (int i = 0; i < RL / 4; ++i) {
-                const float4 k = k4[i];
-                kr[4 * i + 0] = k.x; kr[4 * i + 1] = k.y; kr[4 * i + 2] = k.z; kr[4 * i + 3] = k.w;
-                d0 = fmaf(S[4 * i + 0], k.x, d0); d1 = fmaf(S[4 * i + 1], k.y, d1);
-                d2 = fmaf(S[4 * i + 2], k.z, d2); d3 = fmaf(S[4 * i + 3], k.w, d3);
+                const float4 k = k4[i], q = q4[i];
+                kd[4 * i + 0] = k.x; kd[4 * i + 1] = k.y; kd[4 * i + 2] = k.z; kd[4 * i + 3] = k.w;
+                qd[4 * i + 0] = q.x; qd[4 * i + 1] = q.y; qd[4 * i + 2] = q.z; qd[4 * i + 3] = q.w;
             }
-            float dot = (d0 + d1) + (d2 + d3);
+        };
+        // one token with its q and k in registers; the next token's are fetched into the other pair meanwhile
+        auto step = [&](const float (&kc)[RL], const float (&qc)[RL], float (&kx)[RL], float (&qx)[RL], int t) {
+            if (AHEAD && t + 1 < nc) load(kx, qx, t + 1);
+            const float fd = g_s[t], bt = g_s[CH + t], qn = qn_s[t], kn = kn_s[t], kq = kq_s[t];
+            const float vt = v_s[t * cols + ec];
+            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f, a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < RL / 4; ++i) {
+                d0 = fmaf(S[4 * i + 0], kc[4 * i + 0], d0); a0 = fmaf(S[4 * i + 0], qc[4 * i + 0], a0);
+                d1 = fmaf(S[4 * i + 1], kc[4 * i + 1], d1); a1 = fmaf(S[4 * i + 1], qc[4 * i + 1], a1);
+                d2 = fmaf(S[4 * i + 2], kc[4 * i + 2], d2); a2 = fmaf(S[4 * i + 2], qc[4 * i + 2], a2);
+                d3 = fmaf(S[4 * i + 3], kc[4 * i + 3], d3); a3 = fmaf(S[4 * i + 3], qc[4 * i + 3], a3);
+            }
+            float dot = (d0 + d1) + (d2 + d3), red = (a0 + a1) + (a2 + a3);
             dot += __shfl_xor_sync(0xffffffffu, dot, GD_COLS);
+            red += __shfl_xor_sync(0xffffffffu, red, GD_COLS);
             dot += __shfl_xor_sync(0xffffffffu, dot, 2 * GD_COLS);
+            red += __shfl_xor_sync(0xffffffffu, red, 2 * GD_COLS);
             // S^T k of the faded state is fade times that of the state before; k's unit factor multiplies the sum
             const float u = bt * (vt - fd * dot * kn);
             const float uk = u * kn;
-            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < RL / 4; ++i) {
-                const float4 q = q4[i];
-                S[4 * i + 0] = fmaf(kr[4 * i + 0], uk, fd * S[4 * i + 0]); a0 = fmaf(S[4 * i + 0], q.x, a0);
-                S[4 * i + 1] = fmaf(kr[4 * i + 1], uk, fd * S[4 * i + 1]); a1 = fmaf(S[4 * i + 1], q.y, a1);
-                S[4 * i + 2] = fmaf(kr[4 * i + 2], uk, fd * S[4 * i + 2]); a2 = fmaf(S[4 * i + 2], q.z, a2);
-                S[4 * i + 3] = fmaf(kr[4 * i + 3], uk, fd * S[4 * i + 3]); a3 = fmaf(S[4 * i + 3], q.w, a3);
+            for (int i = 0; i < RL; ++i) S[i] = fmaf(kc[i], uk, fd * S[i]);
+            // the read-out of the state after the write, from the sums over the state before it
+            if (part == 0) o_s[t * cols + ec] = qn * fmaf(uk, kq, fd * red);
+        };
+        if constexpr (AHEAD) {
+            float ka[RL], qa[RL], kb[RL], qb[RL];
+            load(ka, qa, 0);
+            for (int t = 0; t < nc; t += 2) {
+                step(ka, qa, kb, qb, t);
+                if (t + 1 < nc) step(kb, qb, ka, qa, t + 1);
             }
-            float o = (a0 + a1) + (a2 + a3);
-            o += __shfl_xor_sync(0xffffffffu, o, GD_COLS);
-            o += __shfl_xor_sync(0xffffffffu, o, 2 * GD_COLS);
-            if (part == 0) o_s[t * cols + ec] = o * qn;
+        } else {
+            float ka[RL], qa[RL];
+            for (int t = 0; t < nc; ++t) {
+                load(ka, qa, t);
+                step(ka, qa, ka, qa, t);
+            }
         }
         __syncthreads();
         for (int idx = threadIdx.x; idx < nc * cols; idx += blockDim.x) {
@@ -211,8 +237,8 @@ IB_EXPORT int ib_delta_scan(const float* x, long ld, int q_col, int k_col, int v
     const dim3 grid((E + cols - 1) / cols, H, n_requests);
     const bool vec = ((uintptr_t)x % 16) == 0 && (ld % 4) == 0 && (q_col % 4) == 0 && (k_col % 4) == 0 &&
                      (v_col % 4) == 0 && (D % 4) == 0 && (E % 4) == 0;
-    const int dp = rl * GD_PARTS;
-    const size_t smem = (size_t)(2 * ((2 * ch * dp + ch * cols + 2 * ch + 3) & ~3) + ch * cols + 2 * ch) * sizeof(float);
+    const int dp = (rl + GD_PAD) * GD_PARTS;
+    const size_t smem = (size_t)(2 * ((2 * ch * dp + ch * cols + 2 * ch + 3) & ~3) + ch * cols + 3 * ch) * sizeof(float);
 #define IB_GDSCAN(CH, RL, VEC)                                                                                     \
     do {                                                                                                           \
         if (smem > 48 * 1024) {                                                                                    \

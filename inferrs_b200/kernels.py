@@ -45,6 +45,10 @@ _SIGNATURES = {
     "ib_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int,
                                c_void_p, c_void_p, c_void_p],
+    "ib_joint_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
+                               c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "ib_joint_attention_mma_smem": [c_int, c_int, c_int, c_int, c_int],
     "ib_paged_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                    c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                    c_void_p],
@@ -1518,11 +1522,73 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                             ctx.positions, scale, window, out, False)
 
 
+def joint_mma_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, value_dim: int,
+                                  page_size: int, decode_form: bool = False) -> bool:
+    """Whether the tensor-core kernel for joint queries takes these sizes: bfloat16, keys and values of 64 or 128
+    numbers, a page size that divides 64, at most 16 query heads per key/value head, and the queries and two key
+    tiles of all key/value heads within shared memory."""
+    if dtype != torch.bfloat16 or head_dim != value_dim or n_kv_heads <= 0 or n_heads % n_kv_heads:
+        return False
+    return _core(torch.bfloat16).ib_joint_attention_mma_smem(n_heads, n_kv_heads, head_dim, page_size,
+                                                             int(decode_form)) > 0
+
+
+def joint_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                        tile_req: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, q_start: torch.Tensor,
+                        positions: torch.Tensor, scale: float, window: Optional[int],
+                        dist_bias: Optional[torch.Tensor], out: torch.Tensor, decode_form: bool, n_splits: int = 1):
+    """Tensor-core attention with joint queries ``q`` [rows, H, kv_heads * D] (see :func:`mix_queries`) and the table
+    ``dist_bias`` [H, L] that is taken off the scores by distance (bfloat16).  Prefill form: tile i holds up to
+    64 / (H / kv_heads) tokens of request tile_req[i] from row tile_row0[i].  Decode form: every tile is one token; its
+    keys are cut ``n_splits`` ways and merged through float32 scratch."""
+    bf = (torch.bfloat16,)
+    _need(q, "q", bf, 3)
+    _need(k_pages, "k_pages", bf, 4)
+    _need(v_pages, "v_pages", bf, 4)
+    _need(out, "out", bf, 2)
+    _need(block_table, "block_table", _I, 2)
+    _need(dist_bias, "dist_bias", (torch.float32,), 2, optional=True)
+    for name, t in (("tile_req", tile_req), ("tile_row0", tile_row0), ("q_start", q_start), ("positions", positions)):
+        _need(t, name, _I, 1)
+    n, nh, dq = q.shape
+    n_pages, nkv, page_size, d = k_pages.shape
+    if dq != nkv * d or v_pages.shape != k_pages.shape or out.shape != (n, nh * d) \
+            or (dist_bias is not None and (dist_bias.shape[0] != nh or dist_bias.shape[1] < 1)):
+        raise KernelError(f"joint_attention_mma: q {tuple(q.shape)}, pages {tuple(k_pages.shape)}, out {tuple(out.shape)}")
+    if not joint_mma_attention_supported(q.dtype, nh, nkv, d, v_pages.shape[3], page_size, decode_form):
+        raise KernelError(f"joint_attention_mma does not take head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
+    if tile_req.shape[0] < n_tiles or tile_row0.shape[0] < n_tiles:
+        raise KernelError("joint_attention_mma: tile arrays are shorter than n_tiles")
+    part_o = part_ml = None
+    if decode_form and n_splits > 1:
+        part_o = torch.empty((n, nh, n_splits, d), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, nh, n_splits, 2), dtype=torch.float32, device=q.device)
+    _check(_core(torch.bfloat16).ib_joint_attention_mma(
+        _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
+        _p(tile_row0), n_tiles, _p(q_start), _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0,
+        _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[1], _p(out), int(decode_form), int(n_splits),
+        _p(part_o), _p(part_ml), _stream()), "joint_attention_mma")
+
+
 def joint_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                     ctx, scale: float, window: Optional[int], dist_bias: Optional[torch.Tensor], out: torch.Tensor):
     """Attention of every row of the step with joint queries (see :func:`mix_queries`): head h's score against a token
     is its product with all of the token's key heads side by side, times ``scale``, minus dist_bias[h, distance];
-    values are those of the head's own group.  Picks the kernel for the sizes."""
+    values are those of the head's own group.  Picks the kernel for the sizes: the tensor-core kernel where it takes
+    them (its decode form for steps of single tokens), else the float32 kernel for any size."""
+    n, nh, dq = q.shape
+    nkv, page_size, d, dv = k_pages.shape[1], k_pages.shape[2], k_pages.shape[3], v_pages.shape[3]
+    if joint_mma_attention_supported(q.dtype, nh, nkv, d, dv, page_size, ctx.decode_only):
+        if ctx.decode_only:
+            splits = decode_splits(ctx.n_requests, nkv, min(ctx.max_kv_len, window) if window and window > 0
+                                   else ctx.max_kv_len)
+            joint_attention_mma(q, k_pages, v_pages, block_table, ctx.row_request, ctx.q_start, ctx.n_requests,
+                                ctx.q_start, ctx.positions, scale, window, dist_bias, out, True, splits)
+        else:
+            tile_req, tile_row0, n_tiles = ctx.attention_tiles(MMA_KEYS // (nh // nkv))
+            joint_attention_mma(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
+                                ctx.positions, scale, window, dist_bias, out, False)
+        return
     paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out,
                             joint=True, dist_bias=dist_bias)
 

@@ -150,6 +150,8 @@ def scan(args) -> dict:
     n = sum(lens)
     if args.mode == "scalar":
         return _scalar_decay_scan(args, lens, dtype)
+    if args.mode == "delta":
+        return _delta_scan(args, lens, dtype)
     ld = 2 * h * d + 2 * h * e
     proj = torch.randn(n, ld, device=dev).to(dtype)
     mode = kernels.SCAN_CHANNEL_DECAY if args.mode == "decay" else kernels.SCAN_SCALAR_GATES
@@ -193,6 +195,84 @@ def _scalar_decay_scan(args, lens, dtype) -> dict:
     return {"kernel": f"scan/scalar/{args.form}", "heads": h, "groups": g, "key_dim": d, "value_dim": e, "rows": n,
             "requests": len(lens), "us": round(us, 2), "GBps": round(byts / us / 1e3, 1),
             "TFLOPs": round(flops / us / 1e6, 2), "us_per_token": round(us / max(lens), 4)}
+
+
+def _delta_scan(args, lens, dtype) -> dict:
+    """The gated delta rule alone: float32 rows of q, k (shared by the ``groups`` heads of a group, made unit vectors
+    by the kernel) and v, a fade and a step size per token and head.  Bytes as for the scan with a scalar decay; the
+    arithmetic is half as much again (S^T k, the write, S^T q: 6 D E per token and head)."""
+    h, d, e, g = args.heads, args.key_dim, args.value_dim, getattr(args, "groups", 0) or args.heads
+    dev = torch.device("cuda")
+    n = sum(lens)
+    x = torch.randn(n, 2 * g * d + h * e, device=dev)
+    gates = torch.rand(n, 2 * h, device=dev) * 0.1 + 0.9
+    state = torch.zeros(len(lens) + 1, h * d * e, device=dev)
+    q_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
+    out = torch.empty(n, h, e, dtype=torch.float32, device=dev)
+    fn = lambda: kernels.delta_scan(x, 0, g * d, 2 * g * d, g, gates[:, :h], gates[:, h:], 1e-6, d ** -0.5, state,  # noqa: E731
+                                    q_start, slots, len(lens), out, d, dtype, max(lens))
+    us = _time(fn, args.iters)
+    byts = n * (2 * g * d + h * e) * 4 + n * 2 * h * 4 + n * h * e * 4 + 2 * len(lens) * h * d * e * 4
+    flops = 6 * n * h * d * e
+    return {"kernel": f"scan/delta/{args.form}", "heads": h, "groups": g, "key_dim": d, "value_dim": e, "rows": n,
+            "requests": len(lens), "us": round(us, 2), "GBps": round(byts / us / 1e3, 1),
+            "TFLOPs": round(flops / us / 1e6, 2), "us_per_token": round(us / max(lens), 4)}
+
+
+def joint(args) -> dict:
+    """The attention with joint queries alone (scores mixed across heads, a penalty by distance, a sliding window):
+    one prompt of ``tokens`` rows after ``context_before`` cached ones, or ``batch`` requests of one token each over
+    ``context`` cached ones.  Arithmetic: 2 D per (row, head, visible key) for every key/value head in the scores and
+    2 D for the values; bytes: every visible key of all key/value heads and value once, the queries and the result."""
+    nh, nkv, d, ps, window = args.heads, args.kv_heads, args.head_dim, args.page_size, args.window or None
+    dev = torch.device("cuda")
+    if args.form == "decode":
+        lens, new = [args.context] * args.batch, [1] * args.batch
+    else:
+        lens, new = [args.context_before + args.tokens], [args.tokens]
+    pages_per = [(n + ps - 1) // ps for n in lens]
+    n_pages = sum(pages_per)
+    table = torch.full((len(lens), max(pages_per)), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages).to(torch.int32)
+    at = 0
+    for r, n in enumerate(pages_per):
+        table[r, :n] = perm[at:at + n]
+        at += n
+    table = table.to(dev)
+    pos_list = [p for n, t in zip(lens, new) for p in range(n - t, n)]
+    positions = torch.tensor(pos_list, dtype=torch.int32, device=dev)
+    row_request = torch.tensor([r for r, t in enumerate(new) for _ in range(t)], dtype=torch.int32, device=dev)
+    q_start = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=dev)
+    n = sum(new)
+    q = torch.randn(n, nh, nkv * d, device=dev).to(torch.bfloat16)
+    k_pages = torch.randn(n_pages, nkv, ps, d, device=dev).to(torch.bfloat16)
+    v_pages = torch.randn(n_pages, nkv, ps, d, device=dev).to(torch.bfloat16)
+    bias = torch.rand(nh, window or max(lens), device=dev)
+    out = torch.empty(n, nh * d, dtype=torch.bfloat16, device=dev)
+    scale = d ** -0.5
+    if args.impl == "generic":
+        fn = lambda: kernels.paged_attention_generic(q, k_pages, v_pages, table, row_request, positions, scale, window,  # noqa: E731
+                                                     out, joint=True, dist_bias=bias)
+    elif args.form == "decode":
+        splits = args.splits or kernels.decode_splits(args.batch, nkv, min(args.context, window or args.context))
+        rows = torch.arange(n, dtype=torch.int32, device=dev)
+        fn = lambda: kernels.joint_attention_mma(q, k_pages, v_pages, table, rows, q_start, n, q_start, positions,  # noqa: E731
+                                                 scale, window, bias, out, True, splits)
+    else:
+        tpt = kernels.MMA_KEYS // (nh // nkv)
+        tile_req = torch.zeros((args.tokens + tpt - 1) // tpt, dtype=torch.int32, device=dev)
+        tile_row0 = torch.arange(0, args.tokens, tpt, dtype=torch.int32, device=dev)
+        fn = lambda: kernels.joint_attention_mma(q, k_pages, v_pages, table, tile_req, tile_row0, tile_req.shape[0],  # noqa: E731
+                                                 q_start, positions, scale, window, bias, out, False)
+    us = _time(fn, args.iters)
+    seen = sum(min(p + 1, window or p + 1) for p in pos_list)                 # (row, visible key) pairs
+    keys_read = sum(min(n_, (window or n_) + t - 1) for n_, t in zip(lens, new))
+    flops = 2 * nh * d * (nkv + 1) * seen
+    byts = 2 * keys_read * (nkv + 1) * d * 2 // 1 + 2 * n * nh * (nkv + 1) * d
+    return {"kernel": f"joint_attention/{args.form}/{args.impl}", "heads": nh, "kv_heads": nkv, "head_dim": d,
+            "window": window or 0, "rows": n, "us": round(us, 2), "GBps": round(byts / us / 1e3, 1),
+            "TFLOPs": round(flops / us / 1e6, 1)}
 
 
 def latent(args) -> dict:
@@ -557,7 +637,7 @@ def main(argv=None) -> int:
     a.add_argument("--iters", type=int, default=20)
     a.set_defaults(fn=attention)
     sc = sub.add_parser("scan")
-    sc.add_argument("--mode", choices=["decay", "gates", "scalar"], default="gates",
+    sc.add_argument("--mode", choices=["decay", "gates", "scalar", "delta"], default="gates",
                     help="a decay per key channel, scalar gates with a running maximum, or one decay per token and head")
     sc.add_argument("--groups", type=int, default=0, help="scalar: groups of heads that share q and k (0: every head its own)")
     sc.add_argument("--form", choices=["decode", "prefill"], default="prefill")
@@ -569,6 +649,22 @@ def main(argv=None) -> int:
     sc.add_argument("--value-dim", type=int, default=128)
     sc.add_argument("--iters", type=int, default=20)
     sc.set_defaults(fn=scan)
+    jo = sub.add_parser("joint")
+    jo.add_argument("--form", choices=["decode", "prefill"], default="prefill")
+    jo.add_argument("--impl", choices=["mma", "generic"], default="mma")
+    jo.add_argument("--batch", type=int, default=8)
+    jo.add_argument("--context", type=int, default=2048)
+    jo.add_argument("--tokens", type=int, default=2048)
+    jo.add_argument("--context-before", type=int, default=0)
+    jo.add_argument("--window", type=int, default=1024, help="0: every earlier key is seen")
+    jo.add_argument("--splits", type=int, default=0)
+    jo.add_argument("--heads", type=int, default=8)
+    jo.add_argument("--kv-heads", type=int, default=2)
+    jo.add_argument("--head-dim", type=int, default=128)
+    jo.add_argument("--page-size", type=int, default=16)
+    jo.add_argument("--iters", type=int, default=20)
+    jo.set_defaults(fn=joint)
+
     la = sub.add_parser("latent")
     la.add_argument("--form", choices=["decode", "prefill"], default="prefill")
     la.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")

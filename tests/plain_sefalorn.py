@@ -42,6 +42,18 @@ def residual_gate(h: torch.Tensor, w: Dict[str, torch.Tensor], name: str) -> tor
 
 
 # ---- mixers ------------------------------------------------------------------------------------------------------
+def fixed_decay_rule(q, k, v, decay, S=None) -> torch.Tensor:
+    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t for q, k [T, H, D], v [T, H, E], decay [H]; S [H, D, E], if
+    given, is where the walk starts and is updated in place."""
+    T, H, D = q.shape
+    S = torch.zeros(H, D, v.shape[2], dtype=q.dtype) if S is None else S
+    o = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    for t in range(T):
+        S.copy_(decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :])
+        o[t] = torch.einsum("hde,hd->he", S, q[t])
+    return o
+
+
 def lightning(h, m: dict, w: Dict[str, torch.Tensor], p: str, eps: float) -> torch.Tensor:
     """Linear attention with a fixed decay per head on silu'd queries, keys and values, walked token by token; the
     heads are normed together."""
@@ -50,14 +62,31 @@ def lightning(h, m: dict, w: Dict[str, torch.Tensor], p: str, eps: float) -> tor
     q = silu(h @ w[f"{p}.q"].T).view(T, H, D)
     k = silu(h @ w[f"{p}.k"].T).view(T, H, D)
     v = silu(h @ w[f"{p}.v"].T).view(T, H, E)
-    decay = torch.tensor(m["decay"], dtype=torch.float64).to(h.dtype)
-    S = torch.zeros(H, D, E, dtype=h.dtype)
-    o = torch.zeros(T, H, E, dtype=h.dtype)
-    for t in range(T):
-        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hde,hd->he", S, q[t])
+    o = fixed_decay_rule(q, k, v, torch.tensor(m["decay"], dtype=torch.float64).to(h.dtype))
     o = rms_unit(o.reshape(T, H * E), eps) * w[f"{p}.norm"]
     return (o * torch.sigmoid(h @ w[f"{p}.g"].T)) @ w[f"{p}.o"].T
+
+
+def mixed_score_attention(q, k, v, positions, scale: float, r1, r2, talk, window: Optional[int]) -> torch.Tensor:
+    """Queries q [n, H, D] that stand at ``positions`` over one sequence's keys k [T, G, D] and values v [T, G, E]
+    (key j at position j): score = q . k * scale - r1_h ln(1 + r2_h (i - j)); the heads' scores mixed by talk [H, H];
+    position i sees 0 <= i - j < window; softmax; values of the head's own group.  [n, H, E]."""
+    n, H, _ = q.shape
+    G, E = k.shape[1], v.shape[2]
+    dist = positions[:, None] - torch.arange(k.shape[0])[None, :]
+    see = dist >= 0
+    if window is not None:
+        see = see & (dist < window)
+    far = dist.clamp(min=0).to(q.dtype)
+    scores = torch.zeros(H, n, k.shape[0], dtype=q.dtype)
+    for head in range(H):
+        scores[head] = (q[:, head] @ k[:, head // (H // G)].T) * scale - r1[head] * torch.log(1.0 + r2[head] * far)
+    mixed = torch.einsum("hg,gij->hij", talk.to(q.dtype), scores)
+    prob = torch.softmax(mixed.masked_fill(~see[None], float("-inf")), dim=-1)
+    out = torch.zeros(n, H, E, dtype=q.dtype)
+    for head in range(H):
+        out[:, head] = prob[head] @ v[:, head // (H // G)]
+    return out
 
 
 def window_attention(h, m: dict, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
@@ -68,23 +97,9 @@ def window_attention(h, m: dict, w: Dict[str, torch.Tensor], p: str) -> torch.Te
     q = (h @ w[f"{p}.q"].T + w[f"{p}.q.b"]).view(T, H, D)
     k = (h @ w[f"{p}.k"].T + w[f"{p}.k.b"]).view(T, G, D)
     v = (h @ w[f"{p}.v"].T + w[f"{p}.v.b"]).view(T, G, E)
-    pos = torch.arange(T)
-    dist = (pos[:, None] - pos[None, :])
-    see = dist >= 0
-    if m.get("mask"):                                   # no mask: every earlier position is seen
-        see = see & (dist < int(m["mask"]["size"]))
-    far = dist.clamp(min=0).to(h.dtype)
-    scores = torch.zeros(H, T, T, dtype=h.dtype)
-    for head in range(H):
-        g = head // (H // G)
-        scores[head] = (q[:, head] @ k[:, g].T) * float(m["scale"]) \
-            - w[f"{p}.r1"][head] * torch.log(1.0 + w[f"{p}.r2"][head] * far)
-    mixed = torch.einsum("hg,gij->hij", w[f"{p}.talk"], scores)
-    mixed = mixed.masked_fill(~see[None], float("-inf"))
-    prob = torch.softmax(mixed, dim=-1)
-    out = torch.zeros(T, H, E, dtype=h.dtype)
-    for head in range(H):
-        out[:, head] = prob[head] @ v[:, head // (H // G)]
+    window = int(m["mask"]["size"]) if m.get("mask") else None      # no mask: every earlier position is seen
+    out = mixed_score_attention(q, k, v, torch.arange(T), float(m["scale"]), w[f"{p}.r1"], w[f"{p}.r2"],
+                                w[f"{p}.talk"], window)
     return out.reshape(T, H * E) @ w[f"{p}.o"].T + w[f"{p}.o.b"]
 
 
@@ -99,6 +114,24 @@ def short_conv(x: torch.Tensor, taps_w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def delta_rule(q, k, v, beta, fade, S=None) -> torch.Tensor:
+    """Per head: S <- fade_t S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t.  q, k [T, G, D] (head h
+    reads group h / (H / G)), v [T, H, E], beta and fade [T, H]; S [H, D, E], if given, is where the walk starts and
+    is updated in place."""
+    T, G, D = q.shape
+    H, E = v.shape[1], v.shape[2]
+    group = torch.arange(H) // (H // G)
+    S = torch.zeros(H, D, E, dtype=q.dtype) if S is None else S
+    o = torch.zeros(T, H, E, dtype=q.dtype)
+    for t in range(T):
+        kt, qt = k[t][group], q[t][group]                                            # [H, D]
+        S.mul_(fade[t][:, None, None])
+        u = beta[t][:, None] * (v[t] - torch.einsum("hde,hd->he", S, kt))
+        S.add_(kt[:, :, None] * u[:, None, :])
+        o[t] = torch.einsum("hde,hd->he", S, qt)
+    return o
+
+
 def gated_delta(h, m: dict, w: Dict[str, torch.Tensor], p: str, eps: float) -> torch.Tensor:
     """The gated delta rule: a matrix state per head that fades, is corrected towards the value at the key, and is
     read after the write."""
@@ -111,15 +144,7 @@ def gated_delta(h, m: dict, w: Dict[str, torch.Tensor], p: str, eps: float) -> t
     k = unit_vector(k)
     beta = torch.sigmoid(h @ w[f"{p}.b"].T)                                          # [T, H]
     fade = torch.exp(-torch.exp(w[f"{p}.A_log"]) * softplus(h @ w[f"{p}.a"].T + w[f"{p}.dt_bias"]))
-    group = torch.arange(H) // (H // G)
-    S = torch.zeros(H, D, E, dtype=h.dtype)
-    o = torch.zeros(T, H, E, dtype=h.dtype)
-    for t in range(T):
-        kt, qt = k[t][group], q[t][group]                                            # [H, D]
-        S = fade[t][:, None, None] * S
-        u = beta[t][:, None] * (v[t] - torch.einsum("hde,hd->he", S, kt))
-        S = S + kt[:, :, None] * u[:, None, :]
-        o[t] = torch.einsum("hde,hd->he", S, qt)
+    o = delta_rule(q, k, v, beta, fade)
     o = rms_unit(o, eps) * w[f"{p}.norm"]
     o = o.reshape(T, H * E) * silu(h @ w[f"{p}.g"].T)
     return o @ w[f"{p}.o"].T
@@ -135,17 +160,22 @@ def expert(h, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
     return (silu(h @ w[f"{p}.gate"].T) * (h @ w[f"{p}.up"].T)) @ w[f"{p}.down"].T
 
 
+def sigmoid_shares(z: torch.Tensor, top: int, scale: float) -> torch.Tensor:
+    """[rows, experts]: for the ``top`` experts with the largest sigmoid(z) their score over the sum of the chosen
+    scores (+ 1e-20) times ``scale``, zero for the others."""
+    best, chosen = torch.topk(torch.sigmoid(z), top, dim=-1)
+    weight = best / (best.sum(dim=-1, keepdim=True) + 1e-20) * scale
+    return torch.zeros_like(z).scatter_(1, chosen, weight)
+
+
 def moe_ff(h, mlp: dict, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
     """Experts chosen by the largest sigmoid scores, weighed by their scores over the chosen scores' sum, times a
     constant."""
     n, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-    score = torch.sigmoid(h @ w[f"{p}.router"].T)
-    best, chosen = torch.topk(score, top, dim=-1)
-    weight = best / (best.sum(dim=-1, keepdim=True) + 1e-20) * float(mlp["router"]["scale"])
+    share = sigmoid_shares(h @ w[f"{p}.router"].T, top, float(mlp["router"]["scale"]))
     out = torch.zeros_like(h)
     for e in range(n):
-        share = (weight * (chosen == e)).sum(dim=-1, keepdim=True)
-        out = out + share * expert(h, w, f"{p}.e{e}")
+        out = out + share[:, e:e + 1] * expert(h, w, f"{p}.e{e}")
     return out
 
 
