@@ -1134,7 +1134,8 @@ def delta_scan(x: torch.Tensor, q_col: int, k_col: int, v_col: int, groups: int,
     group h / (H / groups)); ``fade`` and ``beta`` are [rows, H] views with unit last stride; ``unit_eps`` not None:
     q and k are divided by sqrt(sum of squares + unit_eps) per head; q is multiplied by ``q_scale``; ``out`` float32
     [rows, H, E]; ``state`` float32 [slots, ...] with at least H*D*E numbers per slot, S first.  ``max_rows``: the
-    most rows that a request brings, if the caller knows (1: the form for steps of single tokens)."""
+    most rows that a request brings, if the caller knows (1 or 2: one token after the other; else sixteen tokens at
+    once, which differs from that by float32 rounding alone)."""
     _need(x, "x", (torch.float32,), 2)
     _need(out, "out", (torch.float32,), 3)
     _need(state, "state", (torch.float32,))

@@ -691,6 +691,48 @@ def test_delta_scan_against_the_rule(H, G, D, E, aligned, dtype):
     assert float(state[3].abs().max()) == 0.0           # a slot that no request of the step names is not touched
 
 
+@pytest.mark.parametrize("n", [2, 3, 15, 16, 17, 32, 33, 81])
+@pytest.mark.parametrize("H,G,D,E", [(2, 1, 24, 20), (3, 3, 128, 16)])
+def test_delta_scan_sixteen_at_once_against_one_by_one(n, H, G, D, E):
+    """A prompt portion walked sixteen tokens at once and the same rows as steps of single tokens give the rule's
+    result: lengths around the sixteen, a fade of exactly zero (the state is forgotten there, and nothing may divide
+    by it), step sizes of zero and one, a state that is not zero at the start."""
+    from inferrs_b200 import kernels
+    g = torch.Generator().manual_seed(n * 7 + D)
+    x = torch.randn(n, 2 * G * D + H * E, generator=g)
+    fade = torch.rand(n, H, generator=g) * 0.5 + 0.5
+    beta = torch.rand(n, H, generator=g)
+    if n > 2:
+        fade[n // 2, 0] = 0.0
+        beta[n // 3, H - 1] = 0.0
+        beta[n - 1, 0] = 1.0
+    gates = torch.cat([fade, beta], dim=1).cuda().contiguous()
+    start = torch.randn(H, D, E, generator=g)
+    q = x[:, :G * D].reshape(n, G, D).double()
+    k = x[:, G * D:2 * G * D].reshape(n, G, D).double()
+    v = x[:, 2 * G * D:].reshape(n, H, E).double()
+    S = start.double().clone()
+    want = ps.delta_rule(ps.unit_vector(q) * 0.3, ps.unit_vector(k), v, beta.double(), fade.double(), S)
+    got = {}
+    for form in ("portion", "single"):
+        state = torch.zeros((2, H * D * E), dtype=torch.float32, device="cuda")
+        state[1] = start.reshape(-1).cuda()
+        out = torch.empty((n, H, E), dtype=torch.float32, device="cuda")
+        if form == "portion":
+            kernels.delta_scan(x.cuda(), 0, G * D, 2 * G * D, G, gates[:, :H], gates[:, H:], 1e-6, 0.3, state,
+                               dev([0, n]), dev([1]), 1, out, D, torch.float32, max_rows=n)
+        else:
+            for t in range(n):
+                kernels.delta_scan(x[t:t + 1].cuda(), 0, G * D, 2 * G * D, G, gates[t:t + 1, :H], gates[t:t + 1, H:],
+                                   1e-6, 0.3, state, dev([0, 1]), dev([1]), 1, out[t:t + 1], D, torch.float32,
+                                   max_rows=1)
+        assert rel_err(out, want) < 1e-4, form
+        assert rel_err(state[1].reshape(H, D, E), S) < 1e-4, form
+        assert float(state[0].abs().max()) == 0.0
+        got[form] = out
+    assert rel_err(got["portion"], got["single"].double()) < 1e-5
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_delta_scan_without_unit_vectors(dtype):
     from inferrs_b200 import kernels
@@ -773,13 +815,15 @@ def test_router_by_sigmoid_shares(experts, top, scale):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,D,E", [(3, 40, 24), (1, 10, 7), (6, 32, 64)])
-def test_silu_on_the_way_in_and_one_norm_over_all_heads(H, D, E, dtype):
-    """The pieces that the fixed-decay scan gets for this design: q, k and v through silu as float rows, and after
-    the scan one root mean square over the heads side by side, a weight per number and a sigmoid gate."""
+@pytest.mark.parametrize("spare", [3, 4])
+def test_silu_on_the_way_in_and_one_norm_over_all_heads(H, D, E, spare, dtype):
+    """The pieces that the fixed-decay scan gets for this design: q, k and v through silu as float rows (row lengths
+    that are and are not a multiple of four: the kernel's two forms), and after the scan one root mean square over
+    the heads side by side, a weight per number and a sigmoid gate."""
     from inferrs_b200 import kernels
     g = torch.Generator().manual_seed(D)
     n, hd, he = 11, H * D, H * E
-    proj = torch.randn(n, 2 * hd + 2 * he + 3, generator=g).to(dtype)
+    proj = torch.randn(n, 2 * hd + 2 * he + spare, generator=g).to(dtype)
     x = torch.empty((n, 2 * hd + he), dtype=torch.float32, device="cuda")
     kernels.heads_to_float(proj.cuda(), ((0, 0, H, D, 0, 1.0, True), (hd, hd, H, D, 0, 1.0, True),
                                          (2 * hd, 2 * hd, H, E, 0, 1.0, True)), x, None, None, 0, None)

@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def replay(model_dir, dtype, steps, out_dir, max_tokens):
-    """Feed the steps one at a time, waiting for ``done <step>`` after each, as the contract says."""
+    """Feed the steps one at a time, waiting for ``done <step>`` after each, as the tool expects."""
     p = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype",
                           dtype, "--out", out_dir, "--max-tokens", str(max_tokens)],
                          stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
