@@ -238,6 +238,39 @@ __global__ void head_norm_gate_kernel(const OT* __restrict__ o, long o_row, long
     }
 }
 
+// The same with a block of eight warps per (row, head), for heads of 512 numbers and more (one norm over all of a
+// mixer's heads side by side, for instance): a warp alone would walk the row twice, 32 numbers at a time.
+template <typename OT, typename WT>
+__global__ void head_norm_gate_wide_kernel(const OT* __restrict__ o, long o_row, long o_head,
+                                           const act_t* __restrict__ gate, long ld_gate, const WT* __restrict__ w,
+                                           int w_per_head, int norm_mode, int gate_act, float eps,
+                                           act_t* __restrict__ out, int heads, int e_dim) {
+    __shared__ float red[32];
+    ib_grid_dependency_sync();
+    const int row = blockIdx.x / heads, h = blockIdx.x - row * heads;
+    const OT* src = o + (long)row * o_row + (long)h * o_head;
+    float inv = 1.0f;
+    if (norm_mode) {
+        float ss = 0.0f;
+        for (int e = threadIdx.x; e < e_dim; e += blockDim.x) {
+            const float v = ib_to_float(src[e]);
+            ss += v * v;
+        }
+        ss = ib_block_sum(ss, red);
+        inv = 1.0f / sqrtf(ss / (float)e_dim + eps);
+    }
+    const act_t* g = gate + (long)row * ld_gate + (long)h * e_dim;
+    act_t* dst = out + ((long)row * heads + h) * e_dim;
+    for (int e = threadIdx.x; e < e_dim; e += blockDim.x) {
+        float v = ib_to_float(src[e]) * inv;
+        if (w) v *= ib_to_float(w[w_per_head ? h * e_dim + e : e]);
+        const float z = ib_to_float(g[e]);
+        const float sg = 1.0f / (1.0f + expf(-z));
+        v *= gate_act == 0 ? z * sg : sg;
+        dst[e] = ib_from_float<act_t>(v);
+    }
+}
+
 IB_EXPORT int ib_head_norm_gate(const void* o, int o_is_f32, long o_row, long o_head, const void* gate, long ld_gate,
                                 const void* w, int w_is_f32, int w_per_head, int norm_mode, int gate_act, float eps,
                                 void* out, int n_rows, int heads, int e_dim, cudaStream_t stream) {
@@ -245,6 +278,19 @@ IB_EXPORT int ib_head_norm_gate(const void* o, int o_is_f32, long o_row, long o_
     if (heads <= 0 || e_dim <= 0 || gate == nullptr || gate_act < 0 || gate_act > 1) return IB_ERR_ARGUMENT;
     const int warps = 4;
     const long items = (long)n_rows * heads;
+    if (e_dim >= 512 && items <= 0x7fffffffL) {
+#define IB_HNGW(OT, WT)                                                                                        \
+    ib_launch(head_norm_gate_wide_kernel<OT, WT>, dim3((unsigned)items), 256, 0, stream, (const OT*)o, o_row,  \
+              o_head, (const act_t*)gate, ld_gate, (const WT*)w, w_per_head, norm_mode, gate_act, eps,         \
+              (act_t*)out, heads, e_dim)
+        if (o_is_f32) {
+            if (w_is_f32) IB_HNGW(float, float); else IB_HNGW(float, __nv_bfloat16);
+        } else {
+            if (w_is_f32) IB_HNGW(act_t, float); else IB_HNGW(act_t, __nv_bfloat16);
+        }
+#undef IB_HNGW
+        return ib_launch_status();
+    }
     const dim3 grid((unsigned)((items + warps - 1) / warps));
 #define IB_HNG(OT, WT)                                                                                         \
     ib_launch(head_norm_gate_kernel<OT, WT>, grid, 32 * warps, 0, stream, (const OT*)o, o_row, o_head,        \

@@ -814,7 +814,7 @@ def test_router_by_sigmoid_shares(experts, top, scale):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,D,E", [(3, 40, 24), (1, 10, 7), (6, 32, 64)])
+@pytest.mark.parametrize("H,D,E", [(3, 40, 24), (1, 10, 7), (6, 32, 64), (5, 16, 120)])    # the last: a block per row
 @pytest.mark.parametrize("spare", [3, 4])
 def test_silu_on_the_way_in_and_one_norm_over_all_heads(H, D, E, spare, dtype):
     """The pieces that the fixed-decay scan gets for this design: q, k and v through silu as float rows (row lengths
