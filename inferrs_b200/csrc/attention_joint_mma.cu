@@ -17,7 +17,8 @@
 // times D / 16 steps of mma.sync, the queries' fragments coming from shared memory once per (plane, step).
 //
 // Two forms of the same loop, as in the plain tensor-core kernel:
-//   prefill form : 64 rows (64 / Gq tokens of a prompt portion, Gq heads per key/value head); four warps own 16 rows.
+//   prefill form : 128 rows where the queries of so many fit beside two key tiles, else 64 (rows / Gq tokens of a
+//                  prompt portion, Gq heads per key/value head); a warp owns 16 rows.
 //   decode form  : 16 rows (one token's Gq heads); the four warps take 16 keys each of every tile and the grid's z
 //                  dimension splits the keys further; partial results go to scratch and a second kernel merges them.
 // A row at position p sees keys lo..p of its request (ib_first_visible).
@@ -79,9 +80,11 @@ struct JointMmaParams {
     float scale;
 };
 
-template <int D, bool DECODE>
-__global__ void __launch_bounds__(JM_THREADS) joint_attention_mma_kernel(const JointMmaParams P) {
-    constexpr int ROWS = DECODE ? 16 : 64;
+// PR: the rows of a prefill tile, 64 or 128 (a warp per 16 rows); the decode form has four warps on its 16 rows.
+template <int D, bool DECODE, int PR>
+__global__ void __launch_bounds__(DECODE ? JM_THREADS : PR * 2) joint_attention_mma_kernel(const JointMmaParams P) {
+    constexpr int ROWS = DECODE ? 16 : PR;
+    constexpr int THREADS = DECODE ? JM_THREADS : PR * 2;
     constexpr int ST = JM_STAGES;
     constexpr int CH = D / 8;  // 16-byte chunks per row of a plane
     constexpr float LOG2E = 1.4426950408889634f;
@@ -98,7 +101,7 @@ __global__ void __launch_bounds__(JM_THREADS) joint_attention_mma_kernel(const J
     const int req = P.tile_req[tile], row0 = P.tile_row0[tile];
     if (req < 0) return;                            // a place in a tile list of fixed length that holds no tile
     const int G = P.n_heads / C;                    // query heads per key/value head
-    const int tpt = DECODE ? 1 : (64 / G);
+    const int tpt = DECODE ? 1 : (ROWS / G);
     int n_tok = P.q_start[req + 1] - row0;
     if (n_tok > tpt) n_tok = tpt;
     const int p0 = P.positions[row0];
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(JM_THREADS) joint_attention_mma_kernel(const J
     const int dq = C * D;
 
     // queries of this tile: row r = (token r / G, head r % G of group kvh), plane by plane
-    for (int idx = tid; idx < C * ROWS * CH; idx += JM_THREADS) {
+    for (int idx = tid; idx < C * ROWS * CH; idx += THREADS) {
         const int c = idx / (ROWS * CH), rest = idx - c * (ROWS * CH);
         const int r = rest / CH, ch = rest - r * CH;
         const int ti = r / G, g = r - ti * G;
@@ -128,7 +131,7 @@ __global__ void __launch_bounds__(JM_THREADS) joint_attention_mma_kernel(const J
     auto load_kv = [&](int t, int buf) {
         __nv_bfloat16* dk = sk + buf * C * JM_KEYS * D;
         __nv_bfloat16* dv = sv + buf * JM_KEYS * D;
-        for (int idx = tid; idx < JM_KEYS * CH; idx += JM_THREADS) {
+        for (int idx = tid; idx < JM_KEYS * CH; idx += THREADS) {
             const int kk = idx / CH, ch = idx - kk * CH;
             const int j = t * JM_KEYS + kk;
             bool valid = j <= pmax && j >= lo_min;
@@ -372,20 +375,24 @@ __global__ void joint_attention_merge_kernel(const float* __restrict__ part_o, c
     }
 }
 
-static size_t joint_mma_smem(int d, int c, bool decode) {
-    const int rows = decode ? 16 : 64;
+static size_t joint_mma_smem(int d, int c, bool decode, int prefill_rows = 64) {
+    const int rows = decode ? 16 : prefill_rows;
     size_t bytes = (size_t)(c * rows * d + JM_STAGES * (c + 1) * JM_KEYS * d) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * d + 2 * 4 * 16) * sizeof(float) + (size_t)c * rows * d * sizeof(__nv_bfloat16);
     return decode && merge > bytes ? merge : bytes;
 }
 
-template <int D, bool DECODE>
+// Rows of a prefill tile for these sizes: 128 where the queries of 128 rows and two key tiles fit into shared memory
+// (twice the warps on an SM, every key tile fetched for twice the rows), else 64.
+static int joint_mma_prefill_rows(int d, int c) { return joint_mma_smem(d, c, false, 128) <= 224 * 1024 ? 128 : 64; }
+
+template <int D, bool DECODE, int PR>
 static int launch_joint_mma(const JointMmaParams& P, int n_tiles, cudaStream_t stream) {
-    const size_t smem = joint_mma_smem(D, P.n_kv_heads, DECODE);
+    const size_t smem = joint_mma_smem(D, P.n_kv_heads, DECODE, PR);
     static IbDeviceSet configured;   // the attribute is kept per device; it is set to the most that any call may ask
-    if (const int e = ib_allow_dynamic_smem(configured, joint_attention_mma_kernel<D, DECODE>, 224 * 1024)) return e;
+    if (const int e = ib_allow_dynamic_smem(configured, joint_attention_mma_kernel<D, DECODE, PR>, 224 * 1024)) return e;
     const dim3 grid(n_tiles, P.n_kv_heads, DECODE ? P.n_splits : 1);
-    ib_launch(joint_attention_mma_kernel<D, DECODE>, grid, JM_THREADS, smem, stream, P);
+    ib_launch(joint_attention_mma_kernel<D, DECODE, PR>, grid, DECODE ? JM_THREADS : PR * 2, smem, stream, P);
     return ib_launch_status();
 }
 
@@ -395,6 +402,13 @@ IB_EXPORT int ib_joint_attention_mma_smem(int n_heads, int n_kv_heads, int head_
     if ((head_dim != 64 && head_dim != 128) || JM_KEYS % page_size || n_heads / n_kv_heads > 16) return 0;
     const size_t smem = joint_mma_smem(head_dim, n_kv_heads, decode_form != 0);
     return smem <= 224 * 1024 ? (int)smem : 0;
+}
+
+// The rows of a prefill tile for these sizes (0: sizes that the kernel does not take): a tile holds this many divided by
+// (n_heads / n_kv_heads) tokens of one request.
+IB_EXPORT int ib_joint_attention_mma_rows(int n_heads, int n_kv_heads, int head_dim, int page_size) {
+    if (ib_joint_attention_mma_smem(n_heads, n_kv_heads, head_dim, page_size, 0) == 0) return 0;
+    return joint_mma_prefill_rows(head_dim, n_kv_heads);
 }
 
 // q [n_rows, n_heads, n_kv_heads * head_dim] joint queries; bias [n_heads, bias_len] float or null.
@@ -419,10 +433,13 @@ IB_EXPORT int ib_joint_attention_mma(const void* q, const void* k_pages, const v
     P.n_kv_heads = n_kv_heads; P.window = window; P.n_splits = decode_form ? (n_splits < 1 ? 1 : n_splits) : 1;
     P.bias_len = bias_len; P.scale = scale;
     int rc;
+    const bool wide = !decode_form && joint_mma_prefill_rows(head_dim, n_kv_heads) == 128;
     if (head_dim == 64)
-        rc = decode_form ? launch_joint_mma<64, true>(P, n_tiles, stream) : launch_joint_mma<64, false>(P, n_tiles, stream);
+        rc = decode_form ? launch_joint_mma<64, true, 64>(P, n_tiles, stream)
+             : (wide ? launch_joint_mma<64, false, 128>(P, n_tiles, stream) : launch_joint_mma<64, false, 64>(P, n_tiles, stream));
     else
-        rc = decode_form ? launch_joint_mma<128, true>(P, n_tiles, stream) : launch_joint_mma<128, false>(P, n_tiles, stream);
+        rc = decode_form ? launch_joint_mma<128, true, 64>(P, n_tiles, stream)
+             : (wide ? launch_joint_mma<128, false, 128>(P, n_tiles, stream) : launch_joint_mma<128, false, 64>(P, n_tiles, stream));
     if (rc != IB_OK) return rc;
     if (decode_form && P.n_splits > 1) {
         ib_launch(joint_attention_merge_kernel, n_rows * n_heads, head_dim < 128 ? 64 : 128, 0, stream,
@@ -435,6 +452,7 @@ IB_EXPORT int ib_joint_attention_mma(const void* q, const void* k_pages, const v
 #else  // the float32 build has no tensor-core attention: its attention is the generic kernel
 
 IB_EXPORT int ib_joint_attention_mma_smem(int, int, int, int, int) { return 0; }
+IB_EXPORT int ib_joint_attention_mma_rows(int, int, int, int) { return 0; }
 
 IB_EXPORT int ib_joint_attention_mma(const void*, const void*, const void*, const int*, int, int, int, const int*,
                                      const int*, int, const int*, const int*, int, int, int, int, float, int,

@@ -49,6 +49,7 @@ _SIGNATURES = {
                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
                                c_int, c_int, c_void_p, c_void_p, c_void_p],
     "ib_joint_attention_mma_smem": [c_int, c_int, c_int, c_int, c_int],
+    "ib_joint_attention_mma_rows": [c_int, c_int, c_int, c_int],
     "ib_paged_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                    c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                    c_void_p],
@@ -1534,13 +1535,21 @@ def joint_mma_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: 
                                                              int(decode_form)) > 0
 
 
+def joint_mma_prefill_tokens(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> int:
+    """The tokens of one request that a tile of the tensor-core kernel's prefill form holds for these sizes: its rows
+    (128 where the joint queries of so many fit into shared memory, else 64) divided by the heads per key/value
+    head; 0 for sizes that the kernel does not take."""
+    rows = _core(torch.bfloat16).ib_joint_attention_mma_rows(n_heads, n_kv_heads, head_dim, page_size)
+    return rows // (n_heads // n_kv_heads) if rows > 0 else 0
+
+
 def joint_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                         tile_req: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, q_start: torch.Tensor,
                         positions: torch.Tensor, scale: float, window: Optional[int],
                         dist_bias: Optional[torch.Tensor], out: torch.Tensor, decode_form: bool, n_splits: int = 1):
     """Tensor-core attention with joint queries ``q`` [rows, H, kv_heads * D] (see :func:`mix_queries`) and the table
     ``dist_bias`` [H, L] that is taken off the scores by distance (bfloat16).  Prefill form: tile i holds up to
-    64 / (H / kv_heads) tokens of request tile_req[i] from row tile_row0[i].  Decode form: every tile is one token; its
+    :func:`joint_mma_prefill_tokens` tokens of request tile_req[i] from row tile_row0[i].  Decode form: every tile is one token; its
     keys are cut ``n_splits`` ways and merged through float32 scratch."""
     bf = (torch.bfloat16,)
     _need(q, "q", bf, 3)
@@ -1586,7 +1595,7 @@ def joint_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
             joint_attention_mma(q, k_pages, v_pages, block_table, ctx.row_request, ctx.q_start, ctx.n_requests,
                                 ctx.q_start, ctx.positions, scale, window, dist_bias, out, True, splits)
         else:
-            tile_req, tile_row0, n_tiles = ctx.attention_tiles(MMA_KEYS // (nh // nkv))
+            tile_req, tile_row0, n_tiles = ctx.attention_tiles(joint_mma_prefill_tokens(nh, nkv, d, page_size))
             joint_attention_mma(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
                                 ctx.positions, scale, window, dist_bias, out, False)
         return

@@ -260,7 +260,7 @@ def joint(args) -> dict:
         fn = lambda: kernels.joint_attention_mma(q, k_pages, v_pages, table, rows, q_start, n, q_start, positions,  # noqa: E731
                                                  scale, window, bias, out, True, splits)
     else:
-        tpt = kernels.MMA_KEYS // (nh // nkv)
+        tpt = kernels.joint_mma_prefill_tokens(nh, nkv, d, ps)
         tile_req = torch.zeros((args.tokens + tpt - 1) // tpt, dtype=torch.int32, device=dev)
         tile_row0 = torch.arange(0, args.tokens, tpt, dtype=torch.int32, device=dev)
         fn = lambda: kernels.joint_attention_mma(q, k_pages, v_pages, table, tile_req, tile_row0, tile_req.shape[0],  # noqa: E731
