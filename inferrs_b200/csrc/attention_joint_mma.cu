@@ -17,8 +17,8 @@
 // times D / 16 steps of mma.sync, the queries' fragments coming from shared memory once per (plane, step).
 //
 // Two forms of the same loop, as in the plain tensor-core kernel:
-//   prefill form : 128 rows where the queries of so many fit beside two key tiles, else 64 (rows / Gq tokens of a
-//                  prompt portion, Gq heads per key/value head); a warp owns 16 rows.
+//   prefill form : 128 rows (128 / Gq tokens of a prompt portion, Gq heads per key/value head); eight warps own 16
+//                  rows each; two key tiles in shared memory where they fit beside the queries, else one.
 //   decode form  : 16 rows (one token's Gq heads); the four warps take 16 keys each of every tile and the grid's z
 //                  dimension splits the keys further; partial results go to scratch and a second kernel merges them.
 // A row at position p sees keys lo..p of its request (ib_first_visible).
@@ -80,12 +80,12 @@ struct JointMmaParams {
     float scale;
 };
 
-// PR: the rows of a prefill tile, 64 or 128 (a warp per 16 rows); the decode form has four warps on its 16 rows.
-template <int D, bool DECODE, int PR>
+// PR: the rows of a prefill tile (a warp per 16 rows); the decode form has four warps on its 16 rows.
+// ST: key tiles in shared memory, 2 (the next one on its way while this one is worked on) or 1.
+template <int D, bool DECODE, int PR, int ST>
 __global__ void __launch_bounds__(DECODE ? JM_THREADS : PR * 2) joint_attention_mma_kernel(const JointMmaParams P) {
     constexpr int ROWS = DECODE ? 16 : PR;
     constexpr int THREADS = DECODE ? JM_THREADS : PR * 2;
-    constexpr int ST = JM_STAGES;
     constexpr int CH = D / 8;  // 16-byte chunks per row of a plane
     constexpr float LOG2E = 1.4426950408889634f;
     extern __shared__ __align__(128) unsigned char jm_smem[];
@@ -375,32 +375,46 @@ __global__ void joint_attention_merge_kernel(const float* __restrict__ part_o, c
     }
 }
 
-static size_t joint_mma_smem(int d, int c, bool decode, int prefill_rows = 64) {
+static size_t joint_mma_smem(int d, int c, bool decode, int prefill_rows = 64, int stages = JM_STAGES) {
     const int rows = decode ? 16 : prefill_rows;
-    size_t bytes = (size_t)(c * rows * d + JM_STAGES * (c + 1) * JM_KEYS * d) * sizeof(__nv_bfloat16);
+    size_t bytes = (size_t)(c * rows * d + stages * (c + 1) * JM_KEYS * d) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * d + 2 * 4 * 16) * sizeof(float) + (size_t)c * rows * d * sizeof(__nv_bfloat16);
     return decode && merge > bytes ? merge : bytes;
 }
 
 // Rows of a prefill tile for these sizes: 128 where the queries of 128 rows and two key tiles fit into shared memory
 // (twice the warps on an SM, every key tile fetched for twice the rows), else 64.
-static int joint_mma_prefill_rows(int d, int c) { return joint_mma_smem(d, c, false, 128) <= 224 * 1024 ? 128 : 64; }
+// A prefill tile is 128 rows on eight warps.  Where the joint queries of 128 rows leave no room for two key tiles
+// (4 key heads of 128 numbers) one is kept: the fetch then waits for the tile before it to be done with, which costs
+// less than tiles of 64 rows on four warps did (373 us against 524 us for a prompt of 2,048 with 16 heads).
+#define JM_PREFILL_ROWS 128
+static int joint_mma_prefill_stages(int d, int c) {
+    return joint_mma_smem(d, c, false, JM_PREFILL_ROWS, 2) <= 224 * 1024 ? 2 : 1;
+}
 
-template <int D, bool DECODE, int PR>
+template <int D, bool DECODE, int PR, int ST>
 static int launch_joint_mma(const JointMmaParams& P, int n_tiles, cudaStream_t stream) {
-    const size_t smem = joint_mma_smem(D, P.n_kv_heads, DECODE, PR);
+    const size_t smem = joint_mma_smem(D, P.n_kv_heads, DECODE, PR, ST);
     static IbDeviceSet configured;   // the attribute is kept per device; it is set to the most that any call may ask
-    if (const int e = ib_allow_dynamic_smem(configured, joint_attention_mma_kernel<D, DECODE, PR>, 224 * 1024)) return e;
+    if (const int e = ib_allow_dynamic_smem(configured, joint_attention_mma_kernel<D, DECODE, PR, ST>, 224 * 1024)) return e;
     const dim3 grid(n_tiles, P.n_kv_heads, DECODE ? P.n_splits : 1);
-    ib_launch(joint_attention_mma_kernel<D, DECODE, PR>, grid, DECODE ? JM_THREADS : PR * 2, smem, stream, P);
+    ib_launch(joint_attention_mma_kernel<D, DECODE, PR, ST>, grid, DECODE ? JM_THREADS : PR * 2, smem, stream, P);
     return ib_launch_status();
+}
+
+template <int D>
+static int launch_joint_mma_prefill(const JointMmaParams& P, int n_tiles, cudaStream_t stream) {
+    if (joint_mma_prefill_stages(D, P.n_kv_heads) == 2) return launch_joint_mma<D, false, JM_PREFILL_ROWS, 2>(P, n_tiles, stream);
+    return launch_joint_mma<D, false, JM_PREFILL_ROWS, 1>(P, n_tiles, stream);
 }
 
 // The shared memory that a call of these sizes needs (0: sizes that the kernel does not take).
 IB_EXPORT int ib_joint_attention_mma_smem(int n_heads, int n_kv_heads, int head_dim, int page_size, int decode_form) {
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0) return 0;
     if ((head_dim != 64 && head_dim != 128) || JM_KEYS % page_size || n_heads / n_kv_heads > 16) return 0;
-    const size_t smem = joint_mma_smem(head_dim, n_kv_heads, decode_form != 0);
+    const size_t smem = decode_form ? joint_mma_smem(head_dim, n_kv_heads, true)
+                                    : joint_mma_smem(head_dim, n_kv_heads, false, JM_PREFILL_ROWS,
+                                                     joint_mma_prefill_stages(head_dim, n_kv_heads));
     return smem <= 224 * 1024 ? (int)smem : 0;
 }
 
@@ -408,7 +422,7 @@ IB_EXPORT int ib_joint_attention_mma_smem(int n_heads, int n_kv_heads, int head_
 // (n_heads / n_kv_heads) tokens of one request.
 IB_EXPORT int ib_joint_attention_mma_rows(int n_heads, int n_kv_heads, int head_dim, int page_size) {
     if (ib_joint_attention_mma_smem(n_heads, n_kv_heads, head_dim, page_size, 0) == 0) return 0;
-    return joint_mma_prefill_rows(head_dim, n_kv_heads);
+    return JM_PREFILL_ROWS;
 }
 
 // q [n_rows, n_heads, n_kv_heads * head_dim] joint queries; bias [n_heads, bias_len] float or null.
@@ -433,13 +447,10 @@ IB_EXPORT int ib_joint_attention_mma(const void* q, const void* k_pages, const v
     P.n_kv_heads = n_kv_heads; P.window = window; P.n_splits = decode_form ? (n_splits < 1 ? 1 : n_splits) : 1;
     P.bias_len = bias_len; P.scale = scale;
     int rc;
-    const bool wide = !decode_form && joint_mma_prefill_rows(head_dim, n_kv_heads) == 128;
     if (head_dim == 64)
-        rc = decode_form ? launch_joint_mma<64, true, 64>(P, n_tiles, stream)
-             : (wide ? launch_joint_mma<64, false, 128>(P, n_tiles, stream) : launch_joint_mma<64, false, 64>(P, n_tiles, stream));
+        rc = decode_form ? launch_joint_mma<64, true, 64, 2>(P, n_tiles, stream) : launch_joint_mma_prefill<64>(P, n_tiles, stream);
     else
-        rc = decode_form ? launch_joint_mma<128, true, 64>(P, n_tiles, stream)
-             : (wide ? launch_joint_mma<128, false, 128>(P, n_tiles, stream) : launch_joint_mma<128, false, 64>(P, n_tiles, stream));
+        rc = decode_form ? launch_joint_mma<128, true, 64, 2>(P, n_tiles, stream) : launch_joint_mma_prefill<128>(P, n_tiles, stream);
     if (rc != IB_OK) return rc;
     if (decode_form && P.n_splits > 1) {
         ib_launch(joint_attention_merge_kernel, n_rows * n_heads, head_dim < 128 ? 64 : 128, 0, stream,

@@ -1537,8 +1537,7 @@ def joint_mma_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: 
 
 def joint_mma_prefill_tokens(n_heads: int, n_kv_heads: int, head_dim: int, page_size: int) -> int:
     """The tokens of one request that a tile of the tensor-core kernel's prefill form holds for these sizes: its rows
-    (128 where the joint queries of so many fit into shared memory, else 64) divided by the heads per key/value
-    head; 0 for sizes that the kernel does not take."""
+    divided by the heads per key/value head; 0 for sizes that the kernel does not take."""
     rows = _core(torch.bfloat16).ib_joint_attention_mma_rows(n_heads, n_kv_heads, head_dim, page_size)
     return rows // (n_heads // n_kv_heads) if rows > 0 else 0
 

@@ -581,7 +581,7 @@ def test_attention_with_mixed_heads_and_a_distance_penalty(H, G, D, E, window, d
 
 @pytest.mark.parametrize("form", ["prefill", "decode", "decode_split"])
 @pytest.mark.parametrize("H,G,D,window", [(8, 2, 128, 100), (4, 4, 64, 50), (6, 1, 64, None), (3, 3, 128, 1), (16, 1, 64, 129),
-                                          (6, 2, 128, None), (8, 4, 128, 77)])     # the last: tiles of 64 rows
+                                          (6, 2, 128, None), (8, 4, 128, 77)])     # the last: one key tile in shared memory
 def test_tensor_core_attention_with_mixed_heads_and_a_distance_penalty(H, G, D, window, form):
     """The tensor-core kernel for joint queries (bfloat16, keys and values of 64 or 128 numbers) in its prefill form
     (portions after cached tokens, a single token, a first token, tiles that end inside a request) and its decode
@@ -611,8 +611,8 @@ def test_tensor_core_attention_with_mixed_heads_and_a_distance_penalty(H, G, D, 
     out = torch.full((n, H * D), float("nan"), dtype=dtype, device="cuda")
     assert kernels.joint_mma_attention_supported(dtype, H, G, D, D, 16, form != "prefill")
     if form == "prefill":
-        tpt = kernels.joint_mma_prefill_tokens(H, G, D, 16)      # a tile's tokens: by the sizes, 64 or 128 rows
-        assert 0 < tpt * (H // G) <= (64 if (H, G, D) == (8, 4, 128) else 128)
+        tpt = kernels.joint_mma_prefill_tokens(H, G, D, 16)      # a tile's tokens
+        assert 0 < tpt * (H // G) <= 128
         tiles = [(r, row) for r in range(len(new)) for row in range(q_start[r], q_start[r + 1], tpt)]
         tile_req = dev([t[0] for t in tiles] + [-1, -1])           # places that hold no tile are skipped
         tile_row0 = dev([t[1] for t in tiles] + [0, 0])
