@@ -13,7 +13,7 @@ request never reads beyond the tokens it has written.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -45,7 +45,10 @@ class StateNeed:
 class CacheStorage:
     def __init__(self, kv_needs: Dict[int, KVNeed], state_needs: Dict[int, StateNeed], page_size: int,
                  n_pages: int, max_requests: int, dtype: torch.dtype, device: torch.device,
-                 n_pages_per_group: Optional[Sequence[int]] = None):
+                 n_pages_per_group: Optional[Sequence[int]] = None,
+                 side_state_needs: Optional[Dict[Tuple[int, Any], StateNeed]] = None):
+        """``side_state_needs``: per-request states beside a mixer's own, keyed by (cache id, the description that
+        owns the state): the inputs that a short convolution in front of a sub-layer or behind a projection keeps."""
         self.page_size = page_size
         self.max_requests = max_requests
         self.dtype = dtype
@@ -92,6 +95,9 @@ class CacheStorage:
         self.states: Dict[int, torch.Tensor] = {
             cid: torch.zeros((max_requests + 1,) + tuple(need.shape), dtype=need.dtype, device=device)
             for cid, need in state_needs.items()}
+        self.side_states: Dict[Tuple[int, Any], torch.Tensor] = {
+            key: torch.zeros((max_requests + 1,) + tuple(need.shape), dtype=need.dtype, device=device)
+            for key, need in (side_state_needs or {}).items()}
 
     def pages(self, cache_id: int) -> Tuple[torch.Tensor, torch.Tensor, int]:
         """(key pages, value pages, group index) of one cache; pages are [n_pages, kv_heads, page_size, head_dim]
@@ -106,18 +112,27 @@ class CacheStorage:
     def state(self, cache_id: int) -> torch.Tensor:
         return self.states[cache_id]
 
+    def side_state(self, cache_id: int, owner: Any) -> torch.Tensor:
+        """The per-request state [slots, ...] that the description ``owner`` keeps under this cache id."""
+        return self.side_states[(cache_id, owner)]
+
     def clear_slot(self, slot: int):
         """A new request takes the slot: its fixed-size states start at zero."""
-        for t in self.states.values():
+        for t in list(self.states.values()) + list(self.side_states.values()):
             t[slot].zero_()
 
-    def snapshot_states(self) -> Dict[int, torch.Tensor]:
+    def snapshot_states(self) -> Dict[Any, torch.Tensor]:
         """Copies of all fixed-size states (for a caller that has to run a step more than once)."""
-        return {cid: t.clone() for cid, t in self.states.items()}
+        saved = {cid: t.clone() for cid, t in self.states.items()}
+        saved.update({("side",) + key: t.clone() for key, t in self.side_states.items()})
+        return saved
 
-    def restore_states(self, saved: Dict[int, torch.Tensor]):
-        for cid, t in saved.items():
-            self.states[cid].copy_(t)
+    def restore_states(self, saved: Dict[Any, torch.Tensor]):
+        for key, t in saved.items():
+            if isinstance(key, tuple) and key and key[0] == "side":
+                self.side_states[key[1:]].copy_(t)
+            else:
+                self.states[key].copy_(t)
 
     def bytes_per_token(self) -> int:
         """Bytes of keys and values that one token adds, over all groups."""
@@ -128,4 +143,5 @@ class CacheStorage:
     def total_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv) + \
             sum(t.numel() * t.element_size() for t in self.values if t is not None) + \
-            sum(t.numel() * t.element_size() for t in self.states.values())
+            sum(t.numel() * t.element_size() for t in self.states.values()) + \
+            sum(t.numel() * t.element_size() for t in self.side_states.values())

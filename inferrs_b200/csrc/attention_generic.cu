@@ -17,6 +17,11 @@
 // score against a token is the sum of its products with all of the token's key heads; values are still those
 // of the head's own group.  dist_bias [n_heads, bias_len]: dist_bias[h, pos - j] is taken off head h's score
 // against key j (a distance beyond the table reads its last entry).
+//
+// Three more options, each a number per head (absent: not applied).  head_scale[h] multiplies head h's scaled score
+// (a learned temperature).  slopes[h] * (pos - j) is taken off the score (a bias that grows linearly with the
+// distance).  sinks[h]: the softmax's denominator also holds exp(sinks[h]), a place without key and value that
+// counts once per row; it is neither scaled nor biased.
 #include "common.cuh"
 
 #define ATT_WARPS 4
@@ -27,7 +32,8 @@ __global__ void paged_attention_generic_kernel(
     const int* __restrict__ block_table, int max_pages, int page_size, int n_pages,
     const int* __restrict__ row_request, const int* __restrict__ positions, int n_heads, int n_kv_heads,
     int head_dim, int v_dim, float scale, int window, act_t* __restrict__ out,
-    const float* __restrict__ dist_bias, int bias_len) {
+    const float* __restrict__ dist_bias, int bias_len, const float* __restrict__ head_scale,
+    const float* __restrict__ slopes, const float* __restrict__ sinks) {
     extern __shared__ float smem[];
     ib_grid_dependency_sync();
     const int row = blockIdx.x;
@@ -46,6 +52,8 @@ __global__ void paged_attention_generic_kernel(
     const act_t* qr = q + ((long)row * n_heads + head) * dq;
     for (int e = lane; e < dq; e += 32) qs[e] = ib_to_float(qr[e]);
     const float* bias_h = dist_bias ? dist_bias + (long)head * bias_len : nullptr;
+    const float scale_h = head_scale ? scale * head_scale[head] : scale;
+    const float slope_h = slopes ? slopes[head] : 0.0f;
     __syncwarp();
 
     float acc[DPL];
@@ -73,7 +81,7 @@ __global__ void paged_attention_generic_kernel(
                     const act_t* kr = k_pages + off * d;
                     for (int e = 0; e < d; ++e) dot = fmaf(qs[e], ib_to_float(kr[e]), dot);
                 }
-                s = dot * scale;
+                s = dot * scale_h - slope_h * (float)(pos - j);
                 if (bias_h) s -= bias_h[pos - j < bias_len ? pos - j : bias_len - 1];
             }
         }
@@ -97,6 +105,14 @@ __global__ void paged_attention_generic_kernel(
         }
         m = m_new;
     }
+    if (sinks) {        // the place without a key: it adds to the denominator and to nothing else
+        const float sink = sinks[head];
+        const float m_new = fmaxf(m, sink);
+        const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+        l = l * corr + expf(sink - m_new);
+#pragma unroll
+        for (int k = 0; k < DPL; ++k) acc[k] *= corr;
+    }
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
     act_t* dst = out + ((long)row * n_heads + head) * v_dim;
 #pragma unroll
@@ -110,7 +126,8 @@ IB_EXPORT int ib_paged_attention_generic(const void* q, const void* k_pages, con
                                          const int* block_table, int max_pages, int page_size, int n_pages,
                                          const int* row_request, const int* positions, int n_rows, int n_heads,
                                          int n_kv_heads, int head_dim, int v_dim, float scale, int window, void* out,
-                                         int joint, const float* dist_bias, int bias_len, cudaStream_t stream) {
+                                         int joint, const float* dist_bias, int bias_len, const float* head_scale,
+                                         const float* slopes, const float* sinks, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim <= 0 || page_size <= 0 || max_pages <= 0)
         return IB_ERR_ARGUMENT;
@@ -124,7 +141,7 @@ IB_EXPORT int ib_paged_attention_generic(const void* q, const void* k_pages, con
     ib_launch(paged_attention_generic_kernel<DPL, JOINT>, grid, 32 * ATT_WARPS, smem, stream,                   \
         (const act_t*)q, (const act_t*)k_pages, (const act_t*)v_pages, block_table, max_pages, page_size,       \
         n_pages, row_request, positions, n_heads, n_kv_heads, head_dim, v_dim, scale, window, (act_t*)out,      \
-        dist_bias, bias_len)
+        dist_bias, bias_len, head_scale, slopes, sinks)
 #define IB_LAUNCH_ATT(DPL) do { if (joint) IB_LAUNCH_ATT_J(DPL, true); else IB_LAUNCH_ATT_J(DPL, false); } while (0)
     if (v_dim <= 32) IB_LAUNCH_ATT(1);
     else if (v_dim <= 64) IB_LAUNCH_ATT(2);

@@ -11,6 +11,10 @@
 //                  of every tile, and the grid's z dimension splits the keys further; partial results
 //                  (unnormalised sums, row maxima, row sums) go to scratch and a second kernel merges them.
 // A row at position p sees keys lo..p of its request, lo = 0 or p - window + 1.
+//
+// Three options, each a number per head (absent: not applied): head_scale[h] multiplies head h's scaled score,
+// slopes[h] * (p - j) is taken off it, and exp(sinks[h]) joins the softmax's denominator once per row (a place
+// without key and value; with the keys cut over several CTAs it is added where the parts are merged).
 #include "common.cuh"
 
 #if IB_ACT_BF16
@@ -66,7 +70,12 @@ struct AttnMmaParams {
     float* part_ml;                //                          [N, n_heads, splits, 2]
     int max_pages, page_size, n_pages, n_heads, n_kv_heads, window, n_splits;
     float scale_log2;              // scale * log2(e)
+    const float* head_scale;       // [n_heads] or null
+    const float* slopes;           // [n_heads] or null
+    const float* sinks;            // [n_heads] or null
 };
+
+#define AM_LOG2E 1.4426950408889634f
 
 template <int D, bool DECODE>
 __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const AttnMmaParams P) {
@@ -131,10 +140,15 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
     // per-thread rows: ra = base + gid, rb = ra + 8
     const int rbase = DECODE ? 0 : warp * 16;
     int pos_r[2], lo_r[2];
+    float scale_r[2], slope_r[2];      // the row's head: its factor on the score and its slope, both times log2(e)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = rbase + gid + 8 * h;
         const int ti = r / G;
+        const int head = kvh * G + (r - ti * G);
+        const bool head_ok = r - ti * G < G && head < P.n_heads && (DECODE ? r < G : true);
+        scale_r[h] = P.scale_log2 * ((P.head_scale && head_ok) ? P.head_scale[head] : 1.0f);
+        slope_r[h] = (P.slopes && head_ok) ? P.slopes[head] * AM_LOG2E : 0.0f;
         if (ti < n_tok) {
             pos_r[h] = p0 + ti;
             lo_r[h] = ib_first_visible(pos_r[h], P.window);
@@ -204,7 +218,7 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
                 const int h = i >> 1;
                 const int j = t * AM_KEYS + col0 + (i & 1);
                 const bool vis = j >= lo_r[h] && j <= pos_r[h];
-                s[n][i] = vis ? s[n][i] * P.scale_log2 : -INFINITY;
+                s[n][i] = vis ? s[n][i] * scale_r[h] - slope_r[h] * (float)(pos_r[h] - j) : -INFINITY;
                 mx[h] = fmaxf(mx[h], s[n][i]);
             }
         }
@@ -266,7 +280,13 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
             const int r = rbase + gid + 8 * h;
             const int ti = r / G, g = r - ti * G;
             if (ti >= n_tok) continue;
-            const float inv = l_r[h] > 0.0f ? 1.0f / l_r[h] : 0.0f;
+            float inv = l_r[h] > 0.0f ? 1.0f / l_r[h] : 0.0f;
+            if (P.sinks) {     // the place without a key joins the denominator
+                const float sink = P.sinks[kvh * G + g] * AM_LOG2E;
+                const float m_new = fmaxf(m_r[h], sink);
+                const float f = m_r[h] == -INFINITY ? 0.0f : exp2f(m_r[h] - m_new);
+                inv = f / (l_r[h] * f + exp2f(sink - m_new));
+            }
             __nv_bfloat16* dst = P.out + (((long)(row0 + ti) * P.n_heads + kvh * G + g) * D);
 #pragma unroll
             for (int n = 0; n < D / 8; ++n) {
@@ -298,6 +318,9 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + g]);
+        const bool sink_here = P.sinks != nullptr && P.n_splits == 1;      // with splits the merge kernel adds it
+        const float sink = sink_here ? P.sinks[kvh * G + g] * AM_LOG2E : -INFINITY;
+        M = fmaxf(M, sink);
         float acc = 0.0f, L = 0.0f;
         if (M > -INFINITY) {
 #pragma unroll
@@ -306,6 +329,7 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
                 acc += f * so[(w * 16 + g) * D + e];
                 L += f * sl[w * 16 + g];
             }
+            if (sink_here) L += exp2f(sink - M);
         }
         const long head = (long)row0 * P.n_heads + kvh * G + g;
         if (P.n_splits > 1) {
@@ -322,12 +346,15 @@ __global__ void __launch_bounds__(AM_THREADS) paged_attention_mma_kernel(const A
 
 // out[row, head, :] = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       __nv_bfloat16* __restrict__ out, int n_splits, int head_dim) {
+                                       __nv_bfloat16* __restrict__ out, int n_splits, int head_dim,
+                                       const float* __restrict__ sinks, int n_heads) {
     ib_grid_dependency_sync();
     const long head = blockIdx.x;  // row * n_heads + head
     const float* ml = part_ml + head * n_splits * 2;
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
+    const float sink = sinks ? sinks[head % n_heads] * AM_LOG2E : -INFINITY;
+    M = fmaxf(M, sink);
     for (int e = threadIdx.x; e < head_dim; e += blockDim.x) {
         float acc = 0.0f, L = 0.0f;
         if (M > -INFINITY) {
@@ -336,6 +363,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
                 acc += f * part_o[(head * n_splits + s) * head_dim + e];
                 L += f * ml[2 * s + 1];
             }
+            if (sinks) L += exp2f(sink - M);
         }
         out[head * head_dim + e] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
     }
@@ -359,6 +387,7 @@ IB_EXPORT int ib_paged_attention_mma(const void* q, const void* k_pages, const v
                                      const int* tile_row0, int n_tiles, const int* q_start, const int* positions,
                                      int n_rows, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
                                      void* out, int decode_form, int n_splits, float* part_o, float* part_ml,
+                                     const float* head_scale, const float* slopes, const float* sinks,
                                      cudaStream_t stream) {
     if (n_tiles <= 0) return IB_OK;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || max_pages <= 0)
@@ -372,7 +401,8 @@ IB_EXPORT int ib_paged_attention_mma(const void* q, const void* k_pages, const v
     P.positions = positions; P.out = (__nv_bfloat16*)out; P.part_o = part_o; P.part_ml = part_ml;
     P.max_pages = max_pages; P.page_size = page_size; P.n_pages = n_pages; P.n_heads = n_heads;
     P.n_kv_heads = n_kv_heads; P.window = window; P.n_splits = decode_form ? (n_splits < 1 ? 1 : n_splits) : 1;
-    P.scale_log2 = scale * 1.4426950408889634f;
+    P.scale_log2 = scale * AM_LOG2E;
+    P.head_scale = head_scale; P.slopes = slopes; P.sinks = sinks;
     int rc;
 #define IB_AM_CASE(DD)                                                                   \
     if (head_dim == DD)                                                                  \
@@ -383,7 +413,7 @@ IB_EXPORT int ib_paged_attention_mma(const void* q, const void* k_pages, const v
     if (rc != IB_OK) return rc;
     if (decode_form && P.n_splits > 1) {
         ib_launch(attention_merge_kernel, n_rows * n_heads, head_dim < 128 ? 64 : 128, 0, stream, (const float*)part_o,
-                  (const float*)part_ml, (__nv_bfloat16*)out, P.n_splits, head_dim);
+                  (const float*)part_ml, (__nv_bfloat16*)out, P.n_splits, head_dim, sinks, n_heads);
         return ib_launch_status();
     }
     return IB_OK;
@@ -443,7 +473,7 @@ IB_EXPORT int ib_paged_attention_decode_noalloc(const void* q, const void* k_pag
     const int code = ib_paged_attention_mma(q, k_pages, v_pages, block_table, max_pages, page_size, n_pages,
                                             row_request, q_start, n_rows, q_start, positions, n_rows, n_heads,
                                             n_kv_heads, head_dim, scale, window, out, 1, n_splits, part_o, part_ml,
-                                            stream);
+                                            nullptr, nullptr, nullptr, stream);
     if (code == IB_ERR_UNSUPPORTED) return IB_NOALLOC_ERR_UNSUPPORTED;
     if (code == IB_ERR_ARGUMENT) return IB_NOALLOC_ERR_ARGUMENT;
     return code;
@@ -467,7 +497,7 @@ IB_EXPORT const char* ib_paged_attention_decode_noalloc_strerror(int code) {
 
 IB_EXPORT int ib_paged_attention_mma(const void*, const void*, const void*, const int*, int, int, int, const int*,
                                      const int*, int, const int*, const int*, int, int, int, int, float, int, void*,
-                                     int, int, float*, float*, cudaStream_t) {
+                                     int, int, float*, float*, const float*, const float*, const float*, cudaStream_t) {
     return IB_ERR_UNSUPPORTED;
 }
 

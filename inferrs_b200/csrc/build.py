@@ -35,7 +35,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-
 _CORE_SOURCES = ["elementwise.cu", "qk_rope_store.cu", "attention_generic.cu", "gemm_simt.cu", "sampling.cu",
                  "sample_select.cu", "attention_mma.cu", "attention_tcgen05.cu",
                  "attention_pair_tcgen05.cu", "attention_decode.cu", "streams.cu", "linear_scan.cu",
-                 "attention_latent.cu", "state_mixers.cu", "decay_scan.cu", "delta_scan.cu", "gated_blocks.cu", "attention_joint_mma.cu"]
+                 "attention_latent.cu", "state_mixers.cu", "decay_scan.cu", "delta_scan.cu", "gated_blocks.cu", "attention_joint_mma.cu",
+                 "conv_attention.cu"]
 
 # name -> (sources, extra flags, extra link flags)
 LIBRARIES: Dict[str, dict] = {

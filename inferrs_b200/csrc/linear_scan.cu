@@ -7,6 +7,9 @@
 //       m_t = max(f_t + m_{t-1}, i_t)
 //       S_t = exp(f_t + m_{t-1} - m_t) S_{t-1} + exp(i_t - m_t) k_t v_t^T        (n_t the same with k_t alone)
 //       o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
+//   mode 2, a forget gate per key channel that also decides what is written (HGRN2):
+//       f_t = l + (1 - l) sigmoid(z_t + b),   S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T,   o_t = S_t^T silu(q_t)
+//       l is a lower bound per channel; there is no key: what the gate lets go is what the value fills
 //
 // S is [D, E] per head (D key channels, E value channels).  The state, the gates and every sum are float in both
 // builds; q, k and v come from a projection in act_t.  A request's rows are walked in order, one token after the
@@ -57,7 +60,7 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
     float* q_s = smem;                                  // [CH][Dp]
     float* k_s = q_s + CH * Dp;                         // [CH][Dp]
     float* a_s = k_s + CH * Dp;                         // [CH][Dp]   mode 0: the decays
-    float* v_s = a_s + (MODE == 0 ? CH * Dp : 0);       // [CH][COLS]
+    float* v_s = a_s + (MODE != 1 ? CH * Dp : 0);       // [CH][COLS]
     float* part = v_s + CH * LS_COLS;                   // [CH][n_units][COLS]
     float* npart = part + CH * n_warps * LS_COLS;       // [CH][n_warps]     mode 1
     float* g_s = npart + CH * n_warps;                  // [3][CH]           mode 1: keep, take, exp(-m)
@@ -98,7 +101,8 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
     const bool fetches = CH > 1 || half == 0;
     act_t rq[NT], rk[NT], rv[NT];
     float rg[NT], r_gi = 0.0f, r_gf = 0.0f;
-    const float my_bias = (MODE == 0 && d_ok) ? gate_bias[h * D + d_mine] : 0.0f;
+    const float my_bias = (MODE != 1 && d_ok) ? gate_bias[h * D + d_mine] : 0.0f;
+    const float my_low = (MODE == 2 && d_ok) ? gate_bias[H * D + h * D + d_mine] : 0.0f;      // mode 2: the lower bounds follow the biases
     const int d_in = d_ok ? d_mine : D - 1;
     const int last_row = row1 - 1;
     auto fetch = [&](int c0) {
@@ -108,7 +112,7 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
             const act_t* p = proj + (long)min(c0 + t, last_row) * ld;
             rq[i] = p[q_col + h * D + d_in];
             rk[i] = p[k_col + h * D + d_in];
-            if (MODE == 0) rg[i] = gates[(long)min(c0 + t, last_row) * ld_gates + h * D + d_in];
+            if (MODE != 1) rg[i] = gates[(long)min(c0 + t, last_row) * ld_gates + h * D + d_in];
             const int idx = threadIdx.x + i * blockDim.x;          // the values: [tokens][COLS columns]
             const int vt = min(idx / COLS, CH - 1), ve = min(e0 + (idx % COLS), E - 1);
             rv[i] = proj[(long)min(c0 + vt, last_row) * ld + v_col + h * E + ve];
@@ -128,10 +132,18 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
         for (int i = 0; i < NT; ++i) {
             const int t = CH > 1 ? 2 * i + half : 0;
             if (t < nc && fetches) {
-                q_s[t * Dp + d_mine] = d_ok ? ib_to_float(rq[i]) * q_scale : 0.0f;
-                k_s[t * Dp + d_mine] = d_ok ? ib_to_float(rk[i]) : 0.0f;
-                if (MODE == 0)
-                    a_s[t * Dp + d_mine] = d_ok ? expf(ls_logsigmoid(rg[i] + my_bias) * gate_param) : 1.0f;   // 1 / tau
+                if (MODE == 2) {
+                    const float qv = ib_to_float(rq[i]);
+                    const float f = my_low + (1.0f - my_low) / (1.0f + expf(-(rg[i] + my_bias)));
+                    q_s[t * Dp + d_mine] = d_ok ? qv / (1.0f + expf(-qv)) * q_scale : 0.0f;
+                    k_s[t * Dp + d_mine] = d_ok ? 1.0f - f : 0.0f;
+                    a_s[t * Dp + d_mine] = d_ok ? f : 1.0f;
+                } else {
+                    q_s[t * Dp + d_mine] = d_ok ? ib_to_float(rq[i]) * q_scale : 0.0f;
+                    k_s[t * Dp + d_mine] = d_ok ? ib_to_float(rk[i]) : 0.0f;
+                    if (MODE == 0)
+                        a_s[t * Dp + d_mine] = d_ok ? expf(ls_logsigmoid(rg[i] + my_bias) * gate_param) : 1.0f;   // 1 / tau
+                }
             }
             const int idx = threadIdx.x + i * blockDim.x;
             if (idx < nc * COLS) v_s[idx] = (e0 + (idx % COLS) < E) ? ib_to_float(rv[i]) : 0.0f;
@@ -192,7 +204,7 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
             for (int i = 0; i < RL / 4; ++i) {
                 const float4 q = q4[i], k = k4[i];
                 float4 a;
-                if (MODE == 0) a = a4[i]; else a = make_float4(keep, keep, keep, keep);
+                if (MODE != 1) a = a4[i]; else a = make_float4(keep, keep, keep, keep);
                 S[4 * i + 0] = fmaf(a.x, S[4 * i + 0], k.x * vt); acc0 = fmaf(S[4 * i + 0], q.x, acc0);
                 S[4 * i + 1] = fmaf(a.y, S[4 * i + 1], k.y * vt); acc1 = fmaf(S[4 * i + 1], q.y, acc1);
                 S[4 * i + 2] = fmaf(a.z, S[4 * i + 2], k.z * vt); acc2 = fmaf(S[4 * i + 2], q.z, acc2);
@@ -224,11 +236,13 @@ linear_scan_kernel(const act_t* __restrict__ proj, long ld, int q_col, int k_col
     }
 }
 
-static IbDeviceSet scan_smem_set[16];
+static IbDeviceSet scan_smem_set[32];
 
 // proj [rows, ld] act_t holds q and k as [H, D] and v as [H, E] from columns q_col, k_col, v_col on.
 // gates [rows, ld_gates] float: mode 0 the decay's pre-activations [H, D] (gate_bias [H * D], gate_param = tau);
-// mode 1 the input gate's and then the forget gate's pre-activations [2, H] (gate_bias [2 * H], gate_param = cap).
+// mode 1 the input gate's and then the forget gate's pre-activations [2, H] (gate_bias [2 * H], gate_param = cap);
+// mode 2 the forget gate's pre-activations [H, D] (gate_bias [2, H * D]: the biases and then the lower bounds; k_col is
+// not read, gate_param is not used).
 // out [rows, H, E] float.  state: see the head of the file; slot_stride floats per slot.  max_rows: the most rows
 // that a request brings (1 chooses the form for steps of single tokens; any larger number the chunked form).
 IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int k_col, int v_col, const float* gates,
@@ -237,7 +251,7 @@ IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int
                              int D, int E, int max_rows, cudaStream_t stream) {
     if (n_requests <= 0) return IB_OK;
     if (H <= 0 || D <= 0 || E <= 0 || proj == nullptr || gates == nullptr || gate_bias == nullptr || state == nullptr ||
-        (mode != 0 && mode != 1) || !(gate_param > 0.0f))
+        (mode < 0 || mode > 2) || !(gate_param > 0.0f))
         return IB_ERR_ARGUMENT;
     if (D > 256 || H > 65535 || n_requests > 65535) return IB_ERR_UNSUPPORTED;
     const long need = (long)H * E * D + (mode == 1 ? (long)H * D + H : 0);
@@ -247,7 +261,7 @@ IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int
     // at 2,048 tokens of one request with 16 heads of 128 x 128: 0.48 against 0.62 ms with a decay per channel; with
     // scalar gates 0.96 against 0.72 ms (what a block does once per chunk for all its columns weighs more there), so
     // that mode keeps 32.
-    const int cols = (mode == 0 && max_rows != 1 && (long)((E + LS_COLS - 1) / LS_COLS) * H * n_requests < 120) ? 16 : LS_COLS;
+    const int cols = (mode != 1 && max_rows != 1 && (long)((E + LS_COLS - 1) / LS_COLS) * H * n_requests < 120) ? 16 : LS_COLS;
     const dim3 grid((E + cols - 1) / cols, H, n_requests);
     const float param = mode == 0 ? 1.0f / gate_param : gate_param;
     const int ch = max_rows == 1 ? 1 : LS_CHUNK;
@@ -273,7 +287,9 @@ IB_EXPORT int ib_linear_scan(int mode, const void* proj, long ld, int q_col, int
     do {                                                                                                             \
         if (32 * n_warps <= 256) IB_SCAN_T(MODE, CH, 256, SET); else IB_SCAN_T(MODE, CH, 512, SET + 4);              \
     } while (0)
-    if (mode == 0 && ch == 1) IB_SCAN(0, 1, 0);
+    if (mode == 2 && ch == 1) IB_SCAN(2, 1, 16);
+    else if (mode == 2) IB_SCAN(2, LS_CHUNK, 17);
+    else if (mode == 0 && ch == 1) IB_SCAN(0, 1, 0);
     else if (mode == 0) IB_SCAN(0, LS_CHUNK, 1);
     else if (ch == 1) IB_SCAN(1, 1, 2);
     else IB_SCAN(1, LS_CHUNK, 3);

@@ -17,6 +17,19 @@
 __device__ __forceinline__ float sm_silu(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float sm_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float sm_softplus(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+// the tanh form of gelu: 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+__device__ __forceinline__ float sm_gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+// What a gated feed-forward makes of a gate g and an up value u.  mode 0: g' sigmoid(slope g') (u' + 1) with
+// g' = min(g, limit), u' = clamp(u, -limit, limit); mode 1: gelu_tanh(g) u; mode 2: silu(g) u.
+__device__ __forceinline__ float sm_gate_value(int mode, float g, float u, float limit, float slope) {
+    if (mode == 1) return sm_gelu_tanh(g) * u;
+    if (mode == 2) return sm_silu(g) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sm_sigmoid(slope * g) * (u + 1.0f);
+}
 
 // ---------------------------------------------------------------------------
 // residual[r, :] <- (alpha * residual[r, :] + delta[r, :]) / rms * weight   (in place, float)
@@ -373,14 +386,13 @@ IB_EXPORT int ib_gate_group_norm(const float* y, const void* z, long z_ld, const
 // u' = clamp(gate_up[r, inner + j], -limit, limit)
 // ---------------------------------------------------------------------------
 __global__ void clamped_gate_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner, long total,
-                                    float limit, float slope) {
+                                    float limit, float slope, int mode) {
     ib_grid_dependency_sync();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const long r = i / inner;
         const int j = (int)(i - r * inner);
-        const float g = fminf(ib_to_float(gate_up[r * 2 * inner + j]), limit);
-        const float u = fminf(fmaxf(ib_to_float(gate_up[r * 2 * inner + inner + j]), -limit), limit);
-        out[i] = ib_from_float<act_t>(g * sm_sigmoid(slope * g) * (u + 1.0f));
+        out[i] = ib_from_float<act_t>(sm_gate_value(mode, ib_to_float(gate_up[r * 2 * inner + j]),
+                                                    ib_to_float(gate_up[r * 2 * inner + inner + j]), limit, slope));
     }
 }
 
@@ -390,7 +402,7 @@ __global__ void clamped_gate_kernel(const act_t* __restrict__ gate_up, act_t* __
 struct alignas(16) SmActVec { act_t v[SM_VEC]; };
 
 __global__ void clamped_gate_vec_kernel(const act_t* __restrict__ gate_up, act_t* __restrict__ out, int inner,
-                                        float limit, float slope) {
+                                        float limit, float slope, int mode) {
     ib_grid_dependency_sync();
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= inner / SM_VEC) return;
@@ -399,25 +411,24 @@ __global__ void clamped_gate_vec_kernel(const act_t* __restrict__ gate_up, act_t
     const SmActVec u = reinterpret_cast<const SmActVec*>(gate_up + r * 2 * inner + inner)[j];
     SmActVec o;
 #pragma unroll
-    for (int k = 0; k < SM_VEC; ++k) {
-        const float gv = fminf(ib_to_float(g.v[k]), limit);
-        const float uv = fminf(fmaxf(ib_to_float(u.v[k]), -limit), limit);
-        o.v[k] = ib_from_float<act_t>(gv * sm_sigmoid(slope * gv) * (uv + 1.0f));
-    }
+    for (int k = 0; k < SM_VEC; ++k)
+        o.v[k] = ib_from_float<act_t>(sm_gate_value(mode, ib_to_float(g.v[k]), ib_to_float(u.v[k]), limit, slope));
     reinterpret_cast<SmActVec*>(out + r * inner)[j] = o;
 }
 
+// mode 0: the clamped form (limit > 0); mode 1: gelu_tanh(gate) * up (limit and slope are not read).
 IB_EXPORT int ib_clamped_gate(const void* gate_up, void* out, int n_rows, int inner, float limit, float slope,
-                              cudaStream_t stream) {
+                              int mode, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
-    if (inner <= 0 || !(limit > 0.0f)) return IB_ERR_ARGUMENT;
+    if (inner <= 0 || mode < 0 || mode > 1 || (mode == 0 && !(limit > 0.0f))) return IB_ERR_ARGUMENT;
     if (inner % SM_VEC == 0 && sm_aligned16(gate_up) && sm_aligned16(out)) {
         const int nv = inner / SM_VEC;
         const int threads = nv >= 256 ? 256 : ((nv + 31) / 32) * 32;
         for (int r0 = 0; r0 < n_rows; r0 += 65535) {   // blockIdx.y holds at most 65,535 rows
             const int rows = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
             ib_launch(clamped_gate_vec_kernel, dim3((nv + threads - 1) / threads, rows), threads, 0, stream,
-                      (const act_t*)gate_up + (long)r0 * 2 * inner, (act_t*)out + (long)r0 * inner, inner, limit, slope);
+                      (const act_t*)gate_up + (long)r0 * 2 * inner, (act_t*)out + (long)r0 * inner, inner, limit, slope,
+                      mode);
         }
         return ib_launch_status();
     }
@@ -425,7 +436,7 @@ IB_EXPORT int ib_clamped_gate(const void* gate_up, void* out, int n_rows, int in
     long blocks = (total + 255) / 256;
     if (blocks > 148L * 16) blocks = 148L * 16;
     ib_launch(clamped_gate_kernel, (int)blocks, 256, 0, stream, (const act_t*)gate_up, (act_t*)out, inner, total, limit,
-              slope);
+              slope, mode);
     return ib_launch_status();
 }
 
@@ -434,7 +445,8 @@ IB_EXPORT int ib_clamped_gate(const void* gate_up, void* out, int n_rows, int in
 // the shared expert's gate).  mode 0: weights[r, e] = softmax over the `top` largest of logits[r, :] + bias among
 // themselves for those experts, 0 for the others (equal logits: the lower index wins).  mode 1: the scores are
 // s = sigmoid(logits + bias), the `top` largest scores are chosen (equal scores: the lower index) and
-// weights[r, e] = s_e / (sum of the chosen scores + 1e-20).  Either way the weights are multiplied by `scale`;
+// weights[r, e] = s_e / (sum of the chosen scores + 1e-20).  mode 2: the same with the scores s = softmax(logits +
+// bias) over all experts.  Either way the weights are multiplied by `scale`;
 // weights[r, n_experts] = sigmoid(logits[r, n_experts]).  One warp per row.
 // ---------------------------------------------------------------------------
 __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, const float* __restrict__ bias,
@@ -450,12 +462,21 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, co
     for (int e = lane; e < n_experts; e += 32) w[e] = 0.0f;
     __syncwarp();
     float first = 0.0f, sum = 0.0f;
+    float z_max = -INFINITY, z_den = 1.0f;      // mode 2: the softmax over all experts
+    if (mode == 2) {
+        for (int e = lane; e < n_experts; e += 32) z_max = fmaxf(z_max, z[e] + (bias ? bias[e] : 0.0f));
+        z_max = ib_warp_max(z_max);
+        float d = 0.0f;
+        for (int e = lane; e < n_experts; e += 32) d += expf(z[e] + (bias ? bias[e] : 0.0f) - z_max);
+        z_den = ib_warp_sum(d);
+    }
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int at = 0x7fffffff;
         for (int e = lane; e < n_experts; e += 32) {
             float v = z[e] + (bias ? bias[e] : 0.0f);
             if (mode == 1) v = sm_sigmoid(v);
+            if (mode == 2) v = expf(v - z_max) / z_den;
             if (w[e] == 0.0f && (v > best || (v == best && e < at))) { best = v; at = e; }
         }
 #pragma unroll
@@ -466,14 +487,15 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, co
         }
         if (at == 0x7fffffff) break;        // fewer experts than `top`, or nothing but NaN
         if (k == 0) first = best;
-        sum += mode == 1 ? best : expf(best - first);
+        sum += mode != 0 ? best : expf(best - first);
         if (lane == 0) w[at] = -1.0f;
         __syncwarp();
     }
     for (int e = lane; e < n_experts; e += 32)
         if (w[e] < 0.0f) {
             const float v = z[e] + (bias ? bias[e] : 0.0f);
-            w[e] = (mode == 1 ? sm_sigmoid(v) / (sum + 1e-20f) : expf(v - first) / sum) * scale;
+            w[e] = (mode == 1 ? sm_sigmoid(v) / (sum + 1e-20f)
+                    : mode == 2 ? expf(v - z_max) / z_den / (sum + 1e-20f) : expf(v - first) / sum) * scale;
         }
     if (has_shared && lane == 0) w[n_experts] = sm_sigmoid(z[n_experts]);
 }
@@ -481,7 +503,7 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, long ld, co
 IB_EXPORT int ib_router_topk(const float* logits, long ld, const float* bias, int n_experts, int top, int has_shared,
                              float* weights, int n_rows, int mode, float scale, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
-    if (n_experts <= 0 || top <= 0 || top > n_experts || logits == nullptr || weights == nullptr || mode < 0 || mode > 1 ||
+    if (n_experts <= 0 || top <= 0 || top > n_experts || logits == nullptr || weights == nullptr || mode < 0 || mode > 2 ||
         ld < n_experts + (has_shared ? 1 : 0))
         return IB_ERR_ARGUMENT;
     const int warps = 4;
@@ -497,7 +519,8 @@ IB_EXPORT int ib_router_topk(const float* logits, long ld, const float* bias, in
 // down matrices of all experts, side by side along its inner dimension, is the weighted sum over the chosen.
 // ---------------------------------------------------------------------------
 __global__ void routed_gate_kernel(const act_t* __restrict__ gate_up, const float* __restrict__ weights, int n_weights,
-                                   int n_experts, int ff, act_t* __restrict__ out, int inner, long total) {
+                                   int n_experts, int ff, act_t* __restrict__ out, int inner, long total, int act_mode,
+                                   float limit, float slope) {
     ib_grid_dependency_sync();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
         const long r = i / inner;
@@ -507,8 +530,8 @@ __global__ void routed_gate_kernel(const act_t* __restrict__ gate_up, const floa
         const float wt = weights[r * n_weights + e];
         float v = 0.0f;
         if (wt != 0.0f) {
-            const float g = ib_to_float(gate_up[r * 2 * inner + j]);
-            v = sm_silu(g) * ib_to_float(gate_up[r * 2 * inner + inner + j]) * wt;
+            v = sm_gate_value(act_mode, ib_to_float(gate_up[r * 2 * inner + j]),
+                              ib_to_float(gate_up[r * 2 * inner + inner + j]), limit, slope) * wt;
         }
         out[i] = ib_from_float<act_t>(v);
     }
@@ -518,7 +541,8 @@ __global__ void routed_gate_kernel(const act_t* __restrict__ gate_up, const floa
 // elements (a thread's elements then belong to one expert).  The columns of an expert that the token did not
 // choose are not read.
 __global__ void routed_gate_vec_kernel(const act_t* __restrict__ gate_up, const float* __restrict__ weights,
-                                       int n_weights, int n_experts, int ff, act_t* __restrict__ out, int inner) {
+                                       int n_weights, int n_experts, int ff, act_t* __restrict__ out, int inner,
+                                       int act_mode, float limit, float slope) {
     ib_grid_dependency_sync();
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= inner / SM_VEC) return;
@@ -532,7 +556,8 @@ __global__ void routed_gate_vec_kernel(const act_t* __restrict__ gate_up, const 
         const SmActVec u = reinterpret_cast<const SmActVec*>(gate_up + r * 2 * inner + inner)[j];
 #pragma unroll
         for (int k = 0; k < SM_VEC; ++k)
-            o.v[k] = ib_from_float<act_t>(sm_silu(ib_to_float(g.v[k])) * ib_to_float(u.v[k]) * wt);
+            o.v[k] = ib_from_float<act_t>(sm_gate_value(act_mode, ib_to_float(g.v[k]), ib_to_float(u.v[k]), limit,
+                                                        slope) * wt);
     } else {
 #pragma unroll
         for (int k = 0; k < SM_VEC; ++k) o.v[k] = ib_from_float<act_t>(0.0f);
@@ -540,9 +565,12 @@ __global__ void routed_gate_vec_kernel(const act_t* __restrict__ gate_up, const 
     reinterpret_cast<SmActVec*>(out + r * inner)[j] = o;
 }
 
+// clamped != 0: the experts' activation is the clamped form with `limit` and `slope` instead of silu(g) * u.
 IB_EXPORT int ib_routed_gate(const void* gate_up, const float* weights, int n_weights, int n_experts, int ff, void* out,
-                             int n_rows, int inner, cudaStream_t stream) {
+                             int n_rows, int inner, int clamped, float limit, float slope, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
+    if (clamped && !(limit > 0.0f)) return IB_ERR_ARGUMENT;
+    const int act_mode = clamped ? 0 : 2;
     if (inner <= 0 || ff <= 0 || n_experts <= 0 || (long)n_experts * ff > inner || weights == nullptr ||
         n_weights < n_experts + ((long)n_experts * ff < inner ? 1 : 0))
         return IB_ERR_ARGUMENT;
@@ -553,7 +581,7 @@ IB_EXPORT int ib_routed_gate(const void* gate_up, const float* weights, int n_we
             const int rows = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
             ib_launch(routed_gate_vec_kernel, dim3((nv + threads - 1) / threads, rows), threads, 0, stream,
                       (const act_t*)gate_up + (long)r0 * 2 * inner, weights + (long)r0 * n_weights, n_weights, n_experts,
-                      ff, (act_t*)out + (long)r0 * inner, inner);
+                      ff, (act_t*)out + (long)r0 * inner, inner, act_mode, limit, slope);
         }
         return ib_launch_status();
     }
@@ -561,6 +589,6 @@ IB_EXPORT int ib_routed_gate(const void* gate_up, const float* weights, int n_we
     long blocks = (total + 255) / 256;
     if (blocks > 148L * 16) blocks = 148L * 16;
     ib_launch(routed_gate_kernel, (int)blocks, 256, 0, stream, (const act_t*)gate_up, weights, n_weights, n_experts, ff,
-              (act_t*)out, inner, total);
+              (act_t*)out, inner, total, act_mode, limit, slope);
     return ib_launch_status();
 }

@@ -226,14 +226,16 @@ __global__ void head_norm_gate_kernel(const OT* __restrict__ o, long o_row, long
         ss = ib_warp_sum(ss);
         inv = 1.0f / sqrtf(ss / (float)e_dim + eps);
     }
-    const act_t* g = gate + (long)row * ld_gate + (long)h * e_dim;
+    const act_t* g = gate ? gate + (long)row * ld_gate + (long)h * e_dim : nullptr;     // no gate: the normed heads alone
     act_t* dst = out + ((long)row * heads + h) * e_dim;
     for (int e = lane; e < e_dim; e += 32) {
         float v = ib_to_float(src[e]) * inv;
         if (w) v *= ib_to_float(w[w_per_head ? h * e_dim + e : e]);
-        const float z = ib_to_float(g[e]);
-        const float sg = 1.0f / (1.0f + expf(-z));
-        v *= gate_act == 0 ? z * sg : sg;
+        if (g) {
+            const float z = ib_to_float(g[e]);
+            const float sg = 1.0f / (1.0f + expf(-z));
+            v *= gate_act == 0 ? z * sg : sg;
+        }
         dst[e] = ib_from_float<act_t>(v);
     }
 }
@@ -259,14 +261,16 @@ __global__ void head_norm_gate_wide_kernel(const OT* __restrict__ o, long o_row,
         ss = ib_block_sum(ss, red);
         inv = 1.0f / sqrtf(ss / (float)e_dim + eps);
     }
-    const act_t* g = gate + (long)row * ld_gate + (long)h * e_dim;
+    const act_t* g = gate ? gate + (long)row * ld_gate + (long)h * e_dim : nullptr;
     act_t* dst = out + ((long)row * heads + h) * e_dim;
     for (int e = threadIdx.x; e < e_dim; e += blockDim.x) {
         float v = ib_to_float(src[e]) * inv;
         if (w) v *= ib_to_float(w[w_per_head ? h * e_dim + e : e]);
-        const float z = ib_to_float(g[e]);
-        const float sg = 1.0f / (1.0f + expf(-z));
-        v *= gate_act == 0 ? z * sg : sg;
+        if (g) {
+            const float z = ib_to_float(g[e]);
+            const float sg = 1.0f / (1.0f + expf(-z));
+            v *= gate_act == 0 ? z * sg : sg;
+        }
         dst[e] = ib_from_float<act_t>(v);
     }
 }
@@ -275,7 +279,7 @@ IB_EXPORT int ib_head_norm_gate(const void* o, int o_is_f32, long o_row, long o_
                                 const void* w, int w_is_f32, int w_per_head, int norm_mode, int gate_act, float eps,
                                 void* out, int n_rows, int heads, int e_dim, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
-    if (heads <= 0 || e_dim <= 0 || gate == nullptr || gate_act < 0 || gate_act > 1) return IB_ERR_ARGUMENT;
+    if (heads <= 0 || e_dim <= 0 || gate_act < 0 || gate_act > 1) return IB_ERR_ARGUMENT;      // gate may be absent
     const int warps = 4;
     const long items = (long)n_rows * heads;
     if (e_dim >= 512 && items <= 0x7fffffffL) {

@@ -118,6 +118,25 @@ def cache_needs(spec: ModelSpec):
     return kv, states
 
 
+def side_state_needs(spec: ModelSpec):
+    """Per-request states beside the mixers' own, keyed by (cache id, owning description): what the short
+    convolutions in front of sub-layers and behind projections keep of earlier steps.  Asked of every mixer class and
+    arrangement class that has a static ``side_states`` (mixer: of its description; arrangement: of the layer's),
+    which answers a list of (owner, StateNeed)."""
+    out = {}
+    for e in spec.schedule:
+        layer = spec.layers[e.layer]
+        asked = [(cls, m) for m, cls in _mixers(spec, e.layer)]
+        asked.append((part_class("arrangement", _Arrangement(layer.arrangement)), layer))
+        for cls, d in asked:
+            for owner, need in (cls.side_states(d) if hasattr(cls, "side_states") else ()):
+                key = (e.cache, owner)
+                if key in out and out[key] != need:
+                    raise ModelError(f"the state of {owner!r} under cache {e.cache} is used with different needs")
+                out[key] = need
+    return out
+
+
 def _layer_tensor_names(layer) -> List[str]:
     names = []
     for sub in layer.sublayers:

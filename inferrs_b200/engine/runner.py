@@ -21,7 +21,7 @@ from ..cache.storage import CacheStorage
 from ..parts.spec import ModelSpec
 from ..runtime import Runtime
 from .batch import StepContext, StepEntry, build_context
-from .model import Model, cache_needs
+from .model import Model, cache_needs, side_state_needs
 
 
 class ModelRunner:
@@ -43,7 +43,8 @@ class ModelRunner:
         if n_pages is None:
             n_pages = self._pages_for_fraction(kv_needs, page_size, cache_fraction, max_requests,
                                                min(max_context or spec.max_positions, spec.max_positions))
-        self.storage = CacheStorage(kv_needs, state_needs, page_size, n_pages, max_requests, rt.dtype, rt.device)
+        self.storage = CacheStorage(kv_needs, state_needs, page_size, n_pages, max_requests, rt.dtype, rt.device,
+                                    side_state_needs=side_state_needs(spec))
         self.manager = CacheManager(self.storage.layouts, page_size, self.storage.n_pages, max_requests)
         self.page_size = page_size
         self.steps_run = 0

@@ -39,12 +39,12 @@ _SIGNATURES = {
                               c_void_p, c_void_p, c_void_p, c_void_p],
     "ib_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_int,
-                                   c_void_p],
+                                   c_void_p, c_void_p, c_void_p, c_void_p],
     "ib_gemm_tn_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_long, c_long,
                         c_long, c_void_p],
     "ib_paged_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int,
-                               c_void_p, c_void_p, c_void_p],
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "ib_joint_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
                                c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -94,7 +94,7 @@ _SIGNATURES = {
     "ib_conv_state_shift": [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_long, c_long, c_void_p, c_void_p, c_int,
                             c_void_p],
     "ib_gate_group_norm": [c_void_p, c_void_p, c_long, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
-    "ib_clamped_gate": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p],
+    "ib_clamped_gate": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p],
     "ib_router_topk": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
     "ib_gated_add_layer_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
                                 c_int, c_void_p],
@@ -104,9 +104,17 @@ _SIGNATURES = {
     "ib_mix_queries": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ib_delta_scan": [c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_long, c_float, c_float,
                       c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "ib_routed_gate": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+    "ib_routed_gate": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                       c_void_p],
     "ib_decay_scan": [c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p,
                       c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "ib_causal_conv_rows": [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_long, c_long, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_long, c_int, c_int, c_void_p],
+    "ib_conv_norm_rope_store": [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_long,
+                                c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p,
+                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                                c_void_p, c_void_p],
+    "ib_blend_columns": [c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_void_p, c_int, c_void_p],
     "ib_sample": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_int, c_void_p, c_void_p],
 }
@@ -263,17 +271,18 @@ def stream_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], mix: 
 GATE_SILU, GATE_SIGMOID = 0, 1
 
 
-def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], norm: bool, gate_act: int,
+def head_norm_gate(o: torch.Tensor, gate: Optional[torch.Tensor], weight: Optional[torch.Tensor], norm: bool, gate_act: int,
                    eps: float, out: torch.Tensor):
     """out[r, h*E + e] = o[r, h, e] / rms_h * weight * act(gate[r, h*E + e]) with rms_h = sqrt(mean_e(o[r, h]^2) + eps)
     (``norm`` False: no division).  ``o`` is float32 or the activation dtype, [rows, H, E] or any view of that shape
     whose last stride is 1 (a head-major result is read in place); ``gate`` is a [rows, H*E] view of a wider
-    projection; ``weight`` is None, [E] (shared by the heads) or [H*E]; ``gate_act`` is GATE_SILU or GATE_SIGMOID."""
+    projection, or None (no gate: the normed and weighed heads alone); ``weight`` is None, [E] (shared by the heads) or [H*E]; ``gate_act`` is GATE_SILU or GATE_SIGMOID."""
     act = out.dtype
     if not (o.is_cuda and o.dim() == 3 and o.stride(2) == 1 and o.dtype in (torch.float32, act)):
         raise KernelError(f"head_norm_gate: o must be a CUDA [rows, H, E] view with unit last stride in float32 or {act}")
     n, heads, e_dim = o.shape
-    if not (gate.is_cuda and gate.dtype == act and gate.shape == (n, heads * e_dim) and gate.stride(1) == 1):
+    if gate is not None and not (gate.is_cuda and gate.dtype == act and gate.shape == (n, heads * e_dim)
+                                 and gate.stride(1) == 1):
         raise KernelError(f"head_norm_gate: gate must be a [rows, H*E] view in {act} with unit last stride")
     _need(out, "out", _W, 2)
     _need(weight, "weight", _W, 1, optional=True)
@@ -282,7 +291,8 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.T
                           f"{None if weight is None else tuple(weight.shape)}")
     per_head = int(weight is not None and weight.shape[0] == heads * e_dim and heads > 1)
     _check(_core(act).ib_head_norm_gate(
-        _p(o), int(o.dtype == torch.float32), o.stride(0), o.stride(1), _p(gate), gate.stride(0), _p(weight),
+        _p(o), int(o.dtype == torch.float32), o.stride(0), o.stride(1), _p(gate),
+        0 if gate is None else gate.stride(0), _p(weight),
         int(weight is not None and weight.dtype == torch.float32), per_head, int(bool(norm)), int(gate_act), float(eps),
         _p(out), n, heads, e_dim, _stream()), "head_norm_gate")
 
@@ -331,7 +341,7 @@ def latent_norm_store(proj: torch.Tensor, q_col: int, q_weight: torch.Tensor, cq
         _p(row_request), _p(positions), n, float(eps), _stream()), "latent_norm_store")
 
 
-SCAN_CHANNEL_DECAY, SCAN_SCALAR_GATES = 0, 1
+SCAN_CHANNEL_DECAY, SCAN_SCALAR_GATES, SCAN_FORGET_WRITE = 0, 1, 2
 
 
 def linear_scan(mode: int, proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gates: torch.Tensor,
@@ -343,6 +353,8 @@ def linear_scan(mode: int, proj: torch.Tensor, q_col: int, k_col: int, v_col: in
     SCAN_SCALAR_GATES:   i = c tanh((p + b_i)/c), f = logsigmoid(c tanh((r + b_f)/c)), c = gate_param,
                          m' = max(f + m, i), S = exp(f + m - m') S + exp(i - m') k v^T (n likewise with k),
                          o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+    SCAN_FORGET_WRITE:   f = l + (1 - l) sigmoid(z + b),  S = diag(f) S + (1 - f) v^T,  o = S^T (silu(q) * q_scale);
+                         ``gate_bias`` holds b and then l, [2, H*D]; ``k_col`` is not read
 
     ``proj`` [rows, ld] holds q and k as [H, D] and v as [H, E] from the given columns on; ``gates`` float32 holds z
     [rows, H*D], or p and then r [rows, 2H]; ``out`` is float32 [rows, H, E]; ``state`` float32 [slots, ...] with at
@@ -358,8 +370,11 @@ def linear_scan(mode: int, proj: torch.Tensor, q_col: int, k_col: int, v_col: in
     _need(slots, "slots", _I, 1)
     n, heads, e_dim = out.shape
     d_dim = int(key_dim)
-    width = heads * d_dim if mode == SCAN_CHANNEL_DECAY else 2 * heads
-    if proj.shape[0] != n or gates.shape != (n, width) or gate_bias.shape[0] != width or d_dim <= 0 \
+    width = 2 * heads if mode == SCAN_SCALAR_GATES else heads * d_dim
+    n_bias = 2 * width if mode == SCAN_FORGET_WRITE else width
+    if mode == SCAN_FORGET_WRITE:
+        k_col = q_col
+    if proj.shape[0] != n or gates.shape != (n, width) or gate_bias.shape[0] != n_bias or d_dim <= 0 \
             or max(q_col, k_col) + heads * d_dim > proj.shape[1] or v_col + heads * e_dim > proj.shape[1] \
             or q_start.shape[0] < n_requests + 1 or slots.shape[0] < n_requests:
         raise KernelError(f"linear_scan: proj {tuple(proj.shape)}, gates {tuple(gates.shape)}, out {tuple(out.shape)}")
@@ -541,7 +556,8 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
     given); a normed kind without a weight is divided and nothing else.  ``norm_after_rotation``: the norm comes
     after the rotation instead of before it.  Values may have another size than keys (the last size of ``v_pages``).
 
-    qkv [N, n_heads * d + n_kv_heads * (d + dv)] (queries only when ``store_kv`` is False);
+    qkv [N, at least n_heads * d + n_kv_heads * (d + dv)] (queries only when ``store_kv`` is False; columns behind
+    them, a gate's for instance, are not read);
     pages [n_pages, n_kv_heads, page_size, d or dv]; block_table int32 [R, max_pages].
     """
     act = q_out.dtype
@@ -555,7 +571,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
         _need(v_pages, "v_pages", (act,), 4)
         v_dim = v_pages.shape[3]
     cols = n_heads * head_dim + (n_kv_heads * (head_dim + v_dim) if store_kv else 0)
-    if qkv.shape[1] != cols or q_out.shape != (n, n_heads, head_dim) or positions.shape[0] != n \
+    if qkv.shape[1] < cols or q_out.shape != (n, n_heads, head_dim) or positions.shape[0] != n \
             or row_request.shape[0] != n:
         raise KernelError(f"qk_norm_rope_store: qkv {tuple(qkv.shape)} (want {cols} columns), q_out "
                           f"{tuple(q_out.shape)}, positions {tuple(positions.shape)}")
@@ -590,7 +606,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_di
                               f"{n_kv_heads} heads of {head_dim}")
         max_pages = block_table.shape[1]
     _check(_core(act).ib_qk_norm_rope_store(
-        _p(qkv), cols, n, n_heads, n_kv_heads, head_dim, v_dim, int(store_kv), _p(q_weight), _p(k_weight),
+        _p(qkv), qkv.shape[1], n, n_heads, n_kv_heads, head_dim, v_dim, int(store_kv), _p(q_weight), _p(k_weight),
         int(wdt == torch.float32), flags, float(eps), _p(cos) if rot_dim else None, _p(sin) if rot_dim else None, rot_dim,
         int(bool(interleaved)), table_rows, _p(positions), _p(row_request), _p(block_table) if store_kv else None, max_pages, page_size,
         n_pages, _p(k_pages) if store_kv else None, _p(v_pages) if store_kv else None, _p(q_out), _stream()),
@@ -618,16 +634,26 @@ def span_argument(window: Optional[int], chunk: Optional[int] = None) -> int:
 
 def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                             row_request: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
-                            out: torch.Tensor, joint: bool = False, dist_bias: Optional[torch.Tensor] = None):
+                            out: torch.Tensor, joint: bool = False, dist_bias: Optional[torch.Tensor] = None,
+                            head_scale: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                            sinks: Optional[torch.Tensor] = None):
     """out[r, h*dv:(h+1)*dv] = attention of token r's head h over its request's cached keys lo..pos.  ``window``:
     see :func:`span_argument` (a negative number: chunks).  Values may have another size dv than keys.
 
     ``joint``: ``q`` is [rows, H, kv_heads * d], one vector per key/value head side by side, and a score is the sum
     of its products with all key heads of the token (the form that queries mixed by :func:`mix_queries` take).
     ``dist_bias`` float32 [H, L]: dist_bias[h, pos - j] is taken off head h's score against key j (a distance beyond
-    the table reads its last entry)."""
+    the table reads its last entry).
+
+    ``head_scale`` / ``slopes`` / ``sinks``: float32 [H] each.  Head h's scaled score is multiplied by head_scale[h];
+    slopes[h] * (pos - j) is taken off it; the softmax's denominator also holds exp(sinks[h]) (a place without key
+    and value that counts once, neither scaled nor biased)."""
     act = out.dtype
     _need(q, "q", (act,), 3)
+    for name, t in (("head_scale", head_scale), ("slopes", slopes), ("sinks", sinks)):
+        _need(t, name, (torch.float32,), 1, optional=True)
+        if t is not None and t.shape[0] != q.shape[1]:
+            raise KernelError(f"paged_attention: {name} has {t.shape[0]} numbers for {q.shape[1]} heads")
     _need(k_pages, "k_pages", (act,), 4)
     _need(v_pages, "v_pages", (act,), 4)
     _need(block_table, "block_table", _I, 2)
@@ -649,7 +675,7 @@ def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     _check(_core(act).ib_paged_attention_generic(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(row_request),
         _p(positions), n, nh, nkv, d, dv, float(scale), int(window) if window else 0, _p(out), int(bool(joint)),
-        _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[1], _stream()),
+        _p(dist_bias), 0 if dist_bias is None else dist_bias.shape[1], _p(head_scale), _p(slopes), _p(sinks), _stream()),
         "paged_attention_generic")
 
 
@@ -1005,6 +1031,115 @@ def conv_state_shift(proj: torch.Tensor, conv_col: int, channels: int, taps: int
                                           int(n_requests), _stream()), "conv_state_shift")
 
 
+def causal_conv_rows(x: torch.Tensor, col: int, conv_w: torch.Tensor, state: Optional[torch.Tensor], state_off: int,
+                     q_start: torch.Tensor, slots: torch.Tensor, row_request: torch.Tensor, out: torch.Tensor,
+                     add_input: bool):
+    """out[r, c] = (x[r, col + c] if ``add_input``) + sum_j conv_w[c, j] * input(r - (taps - 1 - j), c) for the
+    channels c < C = conv_w.shape[0]: a causal convolution per channel over a request's rows, the last tap weighing
+    the row itself.  input(t, c) is this step's row t of the same request, or what the request's slot of ``state``
+    keeps from earlier steps: its last taps - 1 inputs, oldest first, [taps - 1, C] float32 from ``state_off`` on
+    (:func:`conv_state_shift` writes them after the step; zeros for a new request).  ``x`` is a [rows, ld] view in
+    the activation dtype with unit last stride; ``out`` [rows, C]."""
+    act = out.dtype
+    _need(conv_w, "conv_w", (torch.float32,), 2)
+    _need(out, "out", _W, 2)
+    _need(q_start, "q_start", _I, 1)
+    _need(slots, "slots", _I, 1)
+    _need(row_request, "row_request", _I, 1)
+    _need(state, "state", (torch.float32,), optional=True)
+    if not (x.is_cuda and x.dtype == act and x.dim() == 2 and x.stride(1) == 1):
+        raise KernelError(f"causal_conv_rows: x must be a CUDA [rows, ld] view in {act} with unit last stride")
+    n = x.shape[0]
+    channels, taps = conv_w.shape
+    if col < 0 or col + channels > x.shape[1] or out.shape != (n, channels) or row_request.shape[0] != n \
+            or (taps > 1 and state is None):
+        raise KernelError(f"causal_conv_rows: x {tuple(x.shape)}, columns {col}.., weights {tuple(conv_w.shape)}, out "
+                          f"{tuple(out.shape)}")
+    _check(_core(act).ib_causal_conv_rows(
+        _p(x), x.stride(0), int(col), channels, taps, _p(conv_w), _p(state), 0 if state is None else state[0].numel(),
+        int(state_off), _p(q_start), _p(slots), _p(row_request), _p(out), out.stride(0), int(bool(add_input)), n,
+        _stream()), "causal_conv_rows")
+
+
+NORM_NONE, NORM_PER_HEAD, NORM_WHOLE = 0, 1, 2
+
+
+def conv_norm_rope_store(proj: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                         conv_w: Optional[torch.Tensor], state: Optional[torch.Tensor], state_off: int,
+                         q_start: torch.Tensor, slots: torch.Tensor, row_request: torch.Tensor, norm_mode: int,
+                         q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                         cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dim: int, positions: torch.Tensor,
+                         block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, q_out: torch.Tensor):
+    """One pass over the first columns q | k | v of ``proj`` [rows, ld] (H heads of D, G heads of D, G heads of E):
+    a causal convolution per channel (``conv_w`` [channels, taps], None: none; earlier steps' inputs from ``state``
+    as in :func:`causal_conv_rows`), then the norms (NORM_PER_HEAD: every head of q and k divided by its root mean
+    square, weights [D] or None; NORM_WHOLE: all of q, and all of k, divided by one root mean square over the whole
+    projection, weights [H * D] and [G * D]), then the rotation of every head's first ``rot_dim`` numbers by position
+    (i with i + rot_dim / 2); q goes to ``q_out`` [rows, H, D], k and v into their pages."""
+    act = q_out.dtype
+    _need(q_out, "q_out", _W, 3)
+    _need(k_pages, "k_pages", (act,), 4)
+    _need(v_pages, "v_pages", (act,), 4)
+    _need(block_table, "block_table", _I, 2)
+    _need(conv_w, "conv_w", (torch.float32,), 2, optional=True)
+    _need(state, "state", (torch.float32,), optional=True)
+    for name, t in (("q_start", q_start), ("slots", slots), ("row_request", row_request), ("positions", positions)):
+        _need(t, name, _I, 1)
+    if not (proj.is_cuda and proj.dtype == act and proj.dim() == 2 and proj.stride(1) == 1):
+        raise KernelError(f"conv_norm_rope_store: proj must be a CUDA [rows, ld] view in {act} with unit last stride")
+    n = proj.shape[0]
+    n_pages, nkv, page_size, d = k_pages.shape
+    v_dim = v_pages.shape[3]
+    channels = n_heads * head_dim + n_kv_heads * (head_dim + v_dim)
+    taps = 0 if conv_w is None else conv_w.shape[1]
+    if (nkv, d) != (n_kv_heads, head_dim) or v_pages.shape[:3] != k_pages.shape[:3] or proj.shape[1] < channels \
+            or q_out.shape != (n, n_heads, head_dim) or (conv_w is not None and conv_w.shape[0] != channels) \
+            or (taps > 1 and state is None) or positions.shape[0] != n or row_request.shape[0] != n:
+        raise KernelError(f"conv_norm_rope_store: proj {tuple(proj.shape)}, pages {tuple(k_pages.shape)} / "
+                          f"{tuple(v_pages.shape)}, q_out {tuple(q_out.shape)}, "
+                          f"weights {None if conv_w is None else tuple(conv_w.shape)}")
+    wdt = None
+    sizes = {NORM_NONE: (None, None), NORM_PER_HEAD: (head_dim, head_dim),
+             NORM_WHOLE: (n_heads * head_dim, n_kv_heads * head_dim)}.get(norm_mode)
+    if sizes is None:
+        raise KernelError(f"conv_norm_rope_store: unknown norm mode {norm_mode}")
+    for name, w, size in (("q_weight", q_weight, sizes[0]), ("k_weight", k_weight, sizes[1])):
+        _need(w, name, _W, 1, optional=norm_mode != NORM_WHOLE)
+        if w is not None:
+            if w.shape[0] != size:
+                raise KernelError(f"conv_norm_rope_store: {name} has {w.shape[0]} numbers, the norm wants {size}")
+            if wdt is not None and w.dtype != wdt:
+                raise KernelError("conv_norm_rope_store: q_weight and k_weight must have the same dtype")
+            wdt = w.dtype
+    table_rows = 0
+    if rot_dim:
+        _need(cos, "cos", (torch.float32,), 2)
+        _need(sin, "sin", (torch.float32,), 2)
+        if cos.shape[1] != rot_dim // 2 or sin.shape != cos.shape:
+            raise KernelError(f"rotation tables {tuple(cos.shape)} do not match rot_dim {rot_dim}")
+        table_rows = cos.shape[0]
+    _check(_core(act).ib_conv_norm_rope_store(
+        _p(proj), proj.stride(0), n, n_heads, n_kv_heads, head_dim, v_dim, taps, _p(conv_w), _p(state),
+        0 if state is None else state[0].numel(), int(state_off), _p(q_start), _p(slots), _p(row_request),
+        int(norm_mode), _p(q_weight), _p(k_weight), int(wdt == torch.float32), float(eps),
+        _p(cos) if rot_dim else None, _p(sin) if rot_dim else None, int(rot_dim), table_rows, _p(positions),
+        _p(block_table), block_table.shape[1], page_size, n_pages, _p(k_pages), _p(v_pages), _p(q_out), _stream()),
+        "conv_norm_rope_store")
+
+
+def blend_columns(x: torch.Tensor, col: int, other: torch.Tensor, weight: torch.Tensor):
+    """x[r, col + c] <- (1 - weight) x[r, col + c] + weight * other[r, c] in place, for the columns of ``other``
+    [rows, C] (any row stride, unit last stride); ``weight`` is one float32 number on the device."""
+    act = x.dtype
+    _need(x, "x", _W, 2)
+    _need(weight, "weight", (torch.float32,))
+    if not (other.is_cuda and other.dtype == act and other.dim() == 2 and other.stride(1) == 1) \
+            or other.shape[0] != x.shape[0] or col < 0 or col + other.shape[1] > x.shape[1] or weight.numel() != 1:
+        raise KernelError(f"blend_columns: x {tuple(x.shape)}, columns {col}.., other {tuple(other.shape)} {other.dtype}")
+    _check(_core(act).ib_blend_columns(_p(x), x.shape[1], int(col), other.shape[1], _p(other), other.stride(0),
+                                       _p(weight), x.shape[0], _stream()), "blend_columns")
+
+
 def gate_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out: torch.Tensor):
     """out = (y * silu(z)) with each of ``groups`` equal consecutive parts of the row divided by its root mean square,
     times ``weight`` (gated first, normed second).  ``y`` float32 [rows, inner]; ``z`` a [rows, inner] view of a
@@ -1021,20 +1156,26 @@ def gate_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, grou
                                          n, _stream()), "gate_group_norm")
 
 
-def clamped_gate(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float):
+GATE_ACT_CLAMPED_SWISH, GATE_ACT_GELU_TANH = 0, 1
+
+
+def clamped_gate(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float,
+                 activation: int = GATE_ACT_CLAMPED_SWISH):
     """out[r, j] = g sigmoid(slope g) (u + 1) with g = min(gate_up[r, j], limit) and
-    u = clamp(gate_up[r, inner + j], -limit, limit)."""
+    u = clamp(gate_up[r, inner + j], -limit, limit).  ``activation`` GATE_ACT_GELU_TANH:
+    out[r, j] = gelu_tanh(gate_up[r, j]) * gate_up[r, inner + j], gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi)
+    (z + 0.044715 z^3))); ``limit`` and ``slope`` are not read."""
     act = out.dtype
     _need(gate_up, "gate_up", (act,), 2)
     _need(out, "out", _W, 2)
     n, inner = out.shape
     if gate_up.shape != (n, 2 * inner):
         raise KernelError(f"clamped_gate: gate_up {tuple(gate_up.shape)} does not match out {tuple(out.shape)}")
-    _check(_core(act).ib_clamped_gate(_p(gate_up), _p(out), n, inner, float(limit), float(slope), _stream()),
-           "clamped_gate")
+    _check(_core(act).ib_clamped_gate(_p(gate_up), _p(out), n, inner, float(limit), float(slope), int(activation),
+                                      _stream()), "clamped_gate")
 
 
-ROUTE_SOFTMAX_OF_CHOSEN, ROUTE_SIGMOID_SHARE = 0, 1
+ROUTE_SOFTMAX_OF_CHOSEN, ROUTE_SIGMOID_SHARE, ROUTE_SOFTMAX_SHARE = 0, 1, 2
 
 
 def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], n_experts: int, top: int, has_shared: bool,
@@ -1042,8 +1183,8 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], n_experts: i
     """weights[r, e] = the softmax over the ``top`` largest of logits[r, :n_experts] + bias, among themselves, for
     those experts and 0 for the others; with ``has_shared`` weights[r, n_experts] = sigmoid(logits[r, n_experts]).
     ``mode`` ROUTE_SIGMOID_SHARE: the scores are sigmoid(logits + bias), the ``top`` largest are chosen and each
-    chosen expert weighs its score over the sum of the chosen scores (+ 1e-20).  The routed weights are multiplied by
-    ``scale``."""
+    chosen expert weighs its score over the sum of the chosen scores (+ 1e-20).  ROUTE_SOFTMAX_SHARE: the same with the
+    scores softmax(logits + bias) over all experts.  The routed weights are multiplied by ``scale``."""
     _need(logits, "logits", (torch.float32,), 2)
     _need(bias, "bias", (torch.float32,), 1, optional=True)
     _need(weights, "weights", (torch.float32,), 2)
@@ -1053,16 +1194,19 @@ def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], n_experts: i
             or not 0 < top <= n_experts:
         raise KernelError(f"router_topk: logits {tuple(logits.shape)}, weights {tuple(weights.shape)}, top {top} of "
                           f"{n_experts}")
-    if mode not in (ROUTE_SOFTMAX_OF_CHOSEN, ROUTE_SIGMOID_SHARE):
+    if mode not in (ROUTE_SOFTMAX_OF_CHOSEN, ROUTE_SIGMOID_SHARE, ROUTE_SOFTMAX_SHARE):
         raise KernelError(f"router_topk: unknown mode {mode}")
     _check(_core(act_dtype).ib_router_topk(_p(logits), logits.shape[1], _p(bias), int(n_experts), int(top),
                                            int(bool(has_shared)), _p(weights), n, int(mode), float(scale), _stream()),
            "router_topk")
 
 
-def routed_gate(gate_up: torch.Tensor, weights: torch.Tensor, n_experts: int, ff: int, out: torch.Tensor):
+def routed_gate(gate_up: torch.Tensor, weights: torch.Tensor, n_experts: int, ff: int, out: torch.Tensor,
+                limit: Optional[float] = None, slope: float = 1.702):
     """out[r, j] = silu(gate_up[r, j]) * gate_up[r, inner + j] * weights[r, e(j)], the experts' columns side by side:
-    e(j) = j / ff for the routed ones, n_experts for the columns after them (a shared expert)."""
+    e(j) = j / ff for the routed ones, n_experts for the columns after them (a shared expert).  With a ``limit`` the
+    experts' activation is the clamped form, g sigmoid(slope g) (u + 1) with g = min(gate, limit) and
+    u = clamp(up, -limit, limit), in place of silu(gate) * up."""
     act = out.dtype
     _need(gate_up, "gate_up", (act,), 2)
     _need(weights, "weights", (torch.float32,), 2)
@@ -1073,7 +1217,8 @@ def routed_gate(gate_up: torch.Tensor, weights: torch.Tensor, n_experts: int, ff
         raise KernelError(f"routed_gate: gate_up {tuple(gate_up.shape)}, weights {tuple(weights.shape)}, out "
                           f"{tuple(out.shape)}")
     _check(_core(act).ib_routed_gate(_p(gate_up), _p(weights), weights.shape[1], int(n_experts), int(ff), _p(out), n,
-                                     inner, _stream()), "routed_gate")
+                                     inner, int(limit is not None), float(limit or 0.0), float(slope), _stream()),
+           "routed_gate")
 
 
 def decay_scan(x: torch.Tensor, q_col: int, k_col: int, v_col: int, groups: int, keep: torch.Tensor,
@@ -1256,11 +1401,17 @@ def decode_splits(n_requests: int, n_kv_heads: int, max_kv_len: int) -> int:
 def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                         tile_req: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, q_start: torch.Tensor,
                         positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor,
-                        decode_form: bool, n_splits: int = 1):
+                        decode_form: bool, n_splits: int = 1, head_scale: Optional[torch.Tensor] = None,
+                        slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None):
     """Tensor-core attention over the pages (bfloat16).  Prefill form: tile i holds up to 64/G tokens of request
     tile_req[i] from row tile_row0[i].  Decode form: every tile is one token; its keys are cut ``n_splits`` ways
-    and merged through float32 scratch."""
+    and merged through float32 scratch.  ``head_scale`` / ``slopes`` / ``sinks`` (float32 [H]): as in
+    :func:`paged_attention_generic`."""
     bf = (torch.bfloat16,)
+    for name, t in (("head_scale", head_scale), ("slopes", slopes), ("sinks", sinks)):
+        _need(t, name, (torch.float32,), 1, optional=True)
+        if t is not None and t.shape[0] != q.shape[1]:
+            raise KernelError(f"paged_attention_mma: {name} has {t.shape[0]} numbers for {q.shape[1]} heads")
     _need(q, "q", bf, 3)
     _need(k_pages, "k_pages", bf, 4)
     _need(v_pages, "v_pages", bf, 4)
@@ -1286,7 +1437,8 @@ def paged_attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.T
     _check(_core(torch.bfloat16).ib_paged_attention_mma(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
         _p(tile_row0), n_tiles, _p(q_start), _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0,
-        _p(out), int(decode_form), int(n_splits), _p(part_o), _p(part_ml), _stream()), "paged_attention_mma")
+        _p(out), int(decode_form), int(n_splits), _p(part_o), _p(part_ml), _p(head_scale), _p(slopes), _p(sinks),
+        _stream()), "paged_attention_mma")
 
 
 _DECODE_COUNTERS = {}  # device index -> zeroed int32 counters of the decode attention kernel
@@ -1473,16 +1625,33 @@ def attention_tcgen05_error(reset: bool = True) -> int:
 
 
 def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
-                    ctx, scale: float, window: Optional[int], out: torch.Tensor):
+                    ctx, scale: float, window: Optional[int], out: torch.Tensor,
+                    head_scale: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                    sinks: Optional[torch.Tensor] = None):
     """Attention of every row of the step over its request's pages; picks the kernel for the sizes.
 
     ``ctx`` is the step's :class:`~inferrs_b200.engine.batch.StepContext` (row_request, positions
-    and what the faster kernels need to cut the work).
+    and what the faster kernels need to cut the work).  ``head_scale`` / ``slopes`` / ``sinks`` (float32 [H], see
+    :func:`paged_attention_generic`): scores with any of them go to the ``mma.sync`` kernel where it takes the sizes
+    and to the float32 kernel otherwise.
     """
     n, nh, d = q.shape
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
+    per_head = dict(head_scale=head_scale, slopes=slopes, sinks=sinks)
     if v_pages.shape[3] != d or not mma_attention_supported(q.dtype, nh, nkv, d, page_size):
-        paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out)
+        paged_attention_generic(q, k_pages, v_pages, block_table, ctx.row_request, ctx.positions, scale, window, out,
+                                **per_head)
+        return
+    if any(t is not None for t in per_head.values()):
+        if ctx.decode_only:
+            splits = decode_splits(ctx.n_requests, nkv, min(ctx.max_kv_len, window) if window and window > 0
+                                   else ctx.max_kv_len)
+            paged_attention_mma(q, k_pages, v_pages, block_table, ctx.row_request, ctx.q_start, ctx.n_requests,
+                                ctx.q_start, ctx.positions, scale, window, out, True, splits, **per_head)
+        else:
+            tile_req, tile_row0, n_tiles = ctx.attention_tiles(MMA_KEYS // (nh // nkv))
+            paged_attention_mma(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
+                                ctx.positions, scale, window, out, False, **per_head)
         return
     # Prompt portions: tiles of 256 rows (two query tiles per CTA) where they still give every SM a CTA, else
     # tiles of 128 rows.  A step that stands for a padded one (before its graph is captured) says so.

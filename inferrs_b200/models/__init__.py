@@ -3,3 +3,4 @@ from . import qwen3  # noqa: F401
 from . import vebonex  # noqa: F401
 from . import tikizen  # noqa: F401
 from . import sefalorn  # noqa: F401
+from . import ruzunex  # noqa: F401

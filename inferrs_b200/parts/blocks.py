@@ -6,6 +6,7 @@ from typing import List, Optional
 import torch
 
 from .. import kernels
+from ..cache.storage import StateNeed
 from .basic import GatedUpdate, Linear, StreamUpdate
 from .registry import register_arrangement
 from .spec import TensorDecl
@@ -85,10 +86,40 @@ class SequentialBlock:
 register_arrangement("sequential", SequentialBlock)
 
 
+class InputConv:
+    """What a sub-layer reads is replaced by itself plus its causal convolution over time, per channel (see
+    :class:`~inferrs_b200.parts.spec.InputConvSpec`).  The sums are float32; the last taps - 1 inputs of every
+    request are kept in its slot of the state that the description owns under the layer's cache id."""
+
+    def __init__(self, spec, weights):
+        if spec.taps < 1:
+            raise ValueError(f"a convolution has at least one tap, got {spec.taps}")
+        self.spec = spec
+        self.weight = weights[spec.weight].to(torch.float32).contiguous()
+
+    @staticmethod
+    def declare(spec) -> List[TensorDecl]:
+        return [TensorDecl(spec.weight, (spec.width, spec.taps), init="uniform:0:0.3")]
+
+    @staticmethod
+    def state_need(spec) -> Optional[StateNeed]:
+        return StateNeed(shape=((spec.taps - 1) * spec.width,)) if spec.taps > 1 else None
+
+    def __call__(self, ctx, cache_id: int, h: torch.Tensor) -> torch.Tensor:
+        s = self.spec
+        state = ctx.storage.side_state(cache_id, s) if s.taps > 1 else None
+        out = torch.empty_like(h)
+        kernels.causal_conv_rows(h, 0, self.weight, state, 0, ctx.q_start, ctx.slots, ctx.row_request, out, True)
+        if state is not None:
+            kernels.conv_state_shift(h, 0, s.width, s.taps, state, 0, ctx.q_start, ctx.slots, ctx.n_requests)
+        return out
+
+
 class HyperConnectionBlock:
     """A block on a residual that is several streams wide, x_1 .. x_S [rows, S, width] in float32.  Every sub-layer has
     a :class:`~inferrs_b200.parts.spec.StreamConnectionSpec`: it reads u = sum_s read[s] x_s through its norm, and
-    its output y comes back as x_t <- sum_s mix[s, t] x_s + gain[t] y, all streams at once from the old ones.
+    its output y comes back as x_t <- sum_s mix[s, t] x_s + gain[t] y, all streams at once from the old ones.  A
+    sub-layer with an ``input_conv`` reads norm(u) plus its short convolution over time.
 
     As in :class:`SequentialBlock` the output is not brought in where the sub-layer ends: the norm kernel that
     follows does the update, the read and the norm in one pass over the streams, so the block hands its last
@@ -107,7 +138,15 @@ class HyperConnectionBlock:
             out += [TensorDecl(c.read, (c.streams,), init=f"uniform:{1.0 / c.streams}:0.1"),
                     TensorDecl(c.gain, (c.streams,), init="uniform:1:0.2"),
                     TensorDecl(c.mix, (c.streams, c.streams), init="identity:0.1")]
+            if s.input_conv is not None:
+                out += InputConv.declare(s.input_conv)
         return out
+
+    @staticmethod
+    def side_states(spec):
+        """The inputs that the sub-layers' convolutions keep, each under its own description."""
+        needs = [(s.input_conv, InputConv.state_need(s.input_conv)) for s in spec.sublayers if s.input_conv is not None]
+        return [(owner, need) for owner, need in needs if need is not None]
 
     def __init__(self, spec, sublayers: List[BuiltSubLayer], weights=None, rt=None):
         if not sublayers:
@@ -126,6 +165,7 @@ class HyperConnectionBlock:
         self.streams = spec.sublayers[0].connection.streams
         if any(s.connection.streams != self.streams for s in spec.sublayers):
             raise ValueError("the sub-layers of a block hang on the same number of streams")
+        self.convs = [InputConv(s.input_conv, weights) if s.input_conv is not None else None for s in spec.sublayers]
 
     def parts(self):
         for s in self.sublayers:
@@ -136,8 +176,10 @@ class HyperConnectionBlock:
         if residual.dim() != 3 or residual.shape[1] != self.streams:
             raise ValueError(f"a hyper-connection block of {self.streams} streams got a residual of shape "
                              f"{tuple(residual.shape)}")
-        for s, (read, gain, mix) in zip(self.sublayers, self.connections):
+        for s, (read, gain, mix), conv in zip(self.sublayers, self.connections, self.convs):
             h = s.norm.add_norm(residual, pending, read=read)
+            if conv is not None:
+                h = conv(ctx, cache_id, h)
             pending = StreamUpdate(s.run(ctx, cache_id, h), mix, gain)
         return pending
 

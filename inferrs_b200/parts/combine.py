@@ -40,6 +40,11 @@ class MixerSum:
         return MixerSum._one_need(spec, "state_need")
 
     @staticmethod
+    def side_states(spec: MixerSumSpec):
+        """What the two mixers keep beside their own state (a convolution's inputs), each under its own description."""
+        return [pair for m, cls in MixerSum._classes(spec) if hasattr(cls, "side_states") for pair in cls.side_states(m)]
+
+    @staticmethod
     def writes_cache(spec: MixerSumSpec) -> bool:
         return all(cls.writes_cache(m) if hasattr(cls, "writes_cache") else True
                    for m, cls in MixerSum._classes(spec)

@@ -17,7 +17,8 @@ class GatedDense:
     (inferrs-models/src/models/attention_utils.rs:94-118; inferrs-kernels/candle-kernels/src/unary.cu:58-61).
     Gate and up weights are stacked at load: one product feeds the gate kernel, or, for a few rows, one
     kernel does both products and the gate.  With the activation ``clamped_swish`` the gate kernel is
-    min(g, limit) sigmoid(slope min(g, limit)) (clamp(u, -limit, limit) + 1)."""
+    min(g, limit) sigmoid(slope min(g, limit)) (clamp(u, -limit, limit) + 1), with ``gelu_tanh`` it is
+    gelu_tanh(g) u."""
 
     graph_safe = True  # launches depend only on shapes, never on the step's host-side values
 
@@ -28,26 +29,30 @@ class GatedDense:
                 TensorDecl(spec.down_proj, (spec.width, spec.inner))]
 
     def __init__(self, spec: GatedDenseSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
-        if spec.activation not in ("silu", "clamped_swish"):
-            raise ValueError(f"gated feed-forward: activation '{spec.activation}' has no kernel (only 'silu' and "
-                             f"'clamped_swish')")
+        if spec.activation not in ("silu", "clamped_swish", "gelu_tanh"):
+            raise ValueError(f"gated feed-forward: activation '{spec.activation}' has no kernel (only 'silu', "
+                             f"'clamped_swish' and 'gelu_tanh')")
         if spec.activation == "clamped_swish" and not (spec.limit is not None and spec.limit > 0):
             raise ValueError(f"gated feed-forward: the clamped activation needs a positive limit, got {spec.limit}")
         self.clamped = spec.activation == "clamped_swish"
+        self.gelu = spec.activation == "gelu_tanh"
         self.spec = spec
         self.rt = rt
         self.gate_up = Linear(fuse_rows([weights[spec.gate_proj], weights[spec.up_proj]]), rt)
         self.down = Linear(weights[spec.down_proj], rt)
 
     def takes_scaled_rows(self, n_rows: int) -> bool:
-        return not self.clamped and self.gate_up.folds_norms(n_rows) and n_rows <= kernels.SWIGLU_MAX_TOKENS
+        return not (self.clamped or self.gelu) and self.gate_up.folds_norms(n_rows) \
+            and n_rows <= kernels.SWIGLU_MAX_TOKENS
 
     def feeds_sink(self, n_rows: int) -> bool:
         return self.down.folds_norms(n_rows)
 
     def forward(self, ctx, h, sink=None):
         a = torch.empty((h.shape[0], self.spec.inner), dtype=self.rt.dtype, device=h.device)
-        if self.clamped:
+        if self.gelu:
+            kernels.clamped_gate(self.gate_up(h), a, 0.0, 0.0, activation=kernels.GATE_ACT_GELU_TANH)
+        elif self.clamped:
             kernels.clamped_gate(self.gate_up(h), a, self.spec.limit, self.spec.slope)
         else:
             kernels.gated_linear(h, self.gate_up.weight, a, self.rt.dtype)
@@ -93,10 +98,19 @@ class RoutedExperts:
             raise ValueError(f"routed experts: {spec.top} of {n} experts cannot be chosen")
         if spec.shared is not None and spec.shared_inner <= 0:
             raise ValueError("routed experts: a shared expert needs its inner size")
-        modes = {"softmax_of_chosen": kernels.ROUTE_SOFTMAX_OF_CHOSEN, "sigmoid_share": kernels.ROUTE_SIGMOID_SHARE}
+        modes = {"softmax_of_chosen": kernels.ROUTE_SOFTMAX_OF_CHOSEN, "sigmoid_share": kernels.ROUTE_SIGMOID_SHARE,
+                 "softmax_share": kernels.ROUTE_SOFTMAX_SHARE}
         if spec.scoring not in modes:
             raise ValueError(f"routed experts: no router scores by '{spec.scoring}'; known: {sorted(modes)}")
         self.mode = modes[spec.scoring]
+        if spec.activation not in ("silu", "clamped_swish"):
+            raise ValueError(f"routed experts: activation '{spec.activation}' has no kernel (only 'silu' and "
+                             f"'clamped_swish')")
+        if spec.activation == "clamped_swish" and not (spec.limit is not None and spec.limit > 0):
+            raise ValueError(f"routed experts: the clamped activation needs a positive limit, got {spec.limit}")
+        if spec.activation == "clamped_swish" and spec.shared is not None:
+            raise ValueError("routed experts: the clamped activation has no form with a shared expert")
+        self.limit = float(spec.limit) if spec.activation == "clamped_swish" else None
         self.spec, self.rt = spec, rt
         self.n_experts = n
         self.has_shared = spec.shared is not None
@@ -124,7 +138,8 @@ class RoutedExperts:
         kernels.router_topk(logits, self.router_bias, self.n_experts, self.spec.top, self.has_shared, share,
                             self.rt.dtype, mode=self.mode, scale=self.spec.route_scale)
         a = torch.empty((n, self.total_inner), dtype=self.rt.dtype, device=h.device)
-        kernels.routed_gate(self.gate_up(h), share, self.n_experts, self.spec.inner, a)
+        kernels.routed_gate(self.gate_up(h), share, self.n_experts, self.spec.inner, a, limit=self.limit,
+                            slope=self.spec.slope)
         return self.down(a)
 
 

@@ -17,8 +17,8 @@ from ..cache.storage import StateNeed
 from ..runtime import Runtime
 from .basic import Linear, build_position, fuse_rows
 from .registry import register_mixer
-from .spec import (ChannelDecayScanSpec, FixedDecayScanSpec, GatedDeltaScanSpec, ScalarGateScanSpec,
-                   StateSpaceScanSpec, TensorDecl)
+from .spec import (ChannelDecayScanSpec, FixedDecayScanSpec, ForgetWriteScanSpec, GatedDeltaScanSpec,
+                   ScalarGateScanSpec, StateSpaceScanSpec, TensorDecl)
 
 
 class _ScanMixer:
@@ -84,6 +84,56 @@ class ChannelDecayScan(_ScanMixer):
         z = self.decay_up(self.decay_down(h), out_dtype=torch.float32)
         return self._run(ctx, cache_id, h, kernels.SCAN_CHANNEL_DECAY, z, self.decay_bias, self.spec.tau,
                          kernels.GATE_SILU)
+
+
+class ForgetWriteScan:
+    """HGRN2 (see :class:`~inferrs_b200.parts.spec.ForgetWriteScanSpec`).  One product gives q and v; the forget
+    gate's pre-activations come out of their product in float32; the scan kernel turns them into the gate with its
+    lower bound and into its complement, which stands where other scans have a key, sends q through silu and runs
+    the recurrence, all in float32; the norm per head with its shared weight is one kernel before the output
+    product.  The state of a slot is the matrices [H, key_dim, value_dim]."""
+
+    graph_safe = True
+
+    @staticmethod
+    def declare(spec: ForgetWriteScanSpec) -> List[TensorDecl]:
+        hd, he = spec.n_heads * spec.key_dim, spec.n_heads * spec.value_dim
+        return [TensorDecl(spec.q_proj, (hd, spec.width)), TensorDecl(spec.f_proj, (hd, spec.width)),
+                TensorDecl(spec.f_bias, (hd,), init="uniform:1:2"), TensorDecl(spec.lower, (hd,), init="uniform:0.4:0.4"),
+                TensorDecl(spec.v_proj, (he, spec.width)), TensorDecl(spec.out_norm, (spec.value_dim,), init="norm"),
+                TensorDecl(spec.o_proj, (spec.width, he))]
+
+    @staticmethod
+    def cache_need(spec):
+        return None
+
+    @staticmethod
+    def state_need(spec: ForgetWriteScanSpec) -> Optional[StateNeed]:
+        return StateNeed(shape=(spec.n_heads * spec.key_dim * spec.value_dim,))
+
+    def __init__(self, spec: ForgetWriteScanSpec, weights: Dict[str, torch.Tensor], rt: Runtime):
+        self.spec, self.rt = spec, rt
+        self.hd = spec.n_heads * spec.key_dim
+        self.qv = Linear(fuse_rows([weights[spec.q_proj], weights[spec.v_proj]]), rt)
+        self.f = Linear(weights[spec.f_proj], rt)
+        self.o = Linear(weights[spec.o_proj], rt)
+        # the gate's biases and then its lower bounds, as the scan kernel takes them
+        self.gate_bias = torch.cat([weights[spec.f_bias].to(torch.float32),
+                                    weights[spec.lower].to(torch.float32)]).contiguous()
+        self.out_norm = weights[spec.out_norm]
+
+    def forward(self, ctx, cache_id: int, h):
+        s = self.spec
+        n = h.shape[0]
+        proj = self.qv(h)
+        z = self.f(h, out_dtype=torch.float32)
+        o = torch.empty((n, s.n_heads, s.value_dim), dtype=torch.float32, device=h.device)
+        kernels.linear_scan(kernels.SCAN_FORGET_WRITE, proj, 0, 0, self.hd, z, self.gate_bias, 1.0, 1.0,
+                            ctx.storage.state(cache_id), ctx.q_start, ctx.slots, ctx.n_requests, o, s.key_dim,
+                            max_rows=ctx.max_q_len)
+        normed = torch.empty((n, s.n_heads * s.value_dim), dtype=self.rt.dtype, device=h.device)
+        kernels.head_norm_gate(o, None, self.out_norm, True, kernels.GATE_SILU, s.eps, normed)
+        return self.o(normed)
 
 
 class ScalarGateScan(_ScanMixer):
@@ -345,6 +395,7 @@ class StateSpaceScan:
 
 register_mixer("channel_decay_scan", ChannelDecayScan)
 register_mixer("fixed_decay_scan", FixedDecayScan)
+register_mixer("forget_write_scan", ForgetWriteScan)
 register_mixer("state_space_scan", StateSpaceScan)
 register_mixer("gated_delta_scan", GatedDeltaScan)
 register_mixer("scalar_gate_scan", ScalarGateScan)

@@ -79,6 +79,22 @@ class AttentionSpec:
     ``distance_bias`` = (r1, r2), two tensors [n_heads]: r1_h ln(1 + r2_h (i - j)) is taken off head h's scaled score
     of query i against key j.  ``head_mix`` [n_heads, n_heads]: after that the heads' scores are mixed,
     score_h <- sum_g mix[h, g] score_g, before mask and softmax (every head still reads the values of its own group).
+
+    ``distance_slopes`` (one constant per head): slope_h (i - j) is taken off head h's scaled score.
+    ``head_scale`` [n_heads]: head h's scaled score is multiplied by a learned number.
+    ``sink`` [n_heads]: the softmax's denominator also holds exp(sink_h), a place without key and value that counts
+    once; it is neither scaled nor biased.
+    ``qkv_conv`` = (q, k, v tensor names, each [channels, ``conv_taps``]): a causal convolution per channel directly
+    behind each projection (the last tap weighs the token itself, zeros before the start, no bias, no activation);
+    the last conv_taps - 1 projected rows of a request belong to its state.
+    ``norm_whole``: ``q_norm`` / ``k_norm`` are taken over the whole projection, all heads at once (their ``size`` is
+    n_heads * head_dim and n_kv_heads * head_dim), instead of per head.
+    ``gate_proj`` [n_heads * value_dim, width]: the heads side by side are multiplied by sigmoid(gate(x)) before
+    ``o_proj``.
+    ``value_publish``: the layer's values of the step's rows, as they are cached, are kept under this name for later
+    layers of the same step.  ``value_blend`` = (name, weight tensor of one number): v <- (1 - w) v + w v_name with
+    the values that an earlier layer published under that name, before v is cached.  ``unused``: tensors that the
+    weight files hold for this layer and that nothing reads.
     """
 
     width: int
@@ -105,12 +121,23 @@ class AttentionSpec:
     o_bias: Optional[str] = None
     distance_bias: Optional[Tuple[str, str]] = None
     head_mix: Optional[str] = None
+    distance_slopes: Optional[Tuple[float, ...]] = None
+    head_scale: Optional[str] = None
+    sink: Optional[str] = None
+    qkv_conv: Optional[Tuple[str, str, str]] = None
+    conv_taps: int = 0
+    norm_whole: bool = False
+    gate_proj: Optional[str] = None
+    value_publish: Optional[str] = None
+    value_blend: Optional[Tuple[str, str]] = None
+    unused: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
 
 
 @dataclass(frozen=True)
 class GatedDenseSpec:
     """down( act(gate(x)) * up(x) ).  ``activation="clamped_swish"``: with g = min(gate(x), limit) and
-    u = clamp(up(x), -limit, limit) the inner rows are g sigmoid(slope g) (u + 1)."""
+    u = clamp(up(x), -limit, limit) the inner rows are g sigmoid(slope g) (u + 1).  ``activation="gelu_tanh"``:
+    act(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))."""
 
     width: int
     inner: int
@@ -131,7 +158,10 @@ class RoutedExpertsSpec:
     (gate, up, down) tensors.  ``shared`` (optional, (gate, up, down, gate vector) with ``shared_inner``): an expert
     that every token uses; its output is added times sigmoid(gate_vector . x).
     ``scoring="sigmoid_share"``: the scores are s = sigmoid(z), the ``top`` largest scores are chosen, and a chosen
-    expert weighs s_e / (sum of the chosen scores + 1e-20).  ``route_scale`` multiplies the routed experts' weights."""
+    expert weighs s_e / (sum of the chosen scores + 1e-20).  ``scoring="softmax_share"``: the same with the scores
+    s = softmax(z) over all experts.  ``route_scale`` multiplies the routed experts' weights.
+    ``activation="clamped_swish"`` (with ``limit`` and ``slope``): an expert is down_e( g sigmoid(slope g) (u + 1) )
+    with g = min(gate_e(x), limit) and u = clamp(up_e(x), -limit, limit)."""
 
     width: int
     inner: int
@@ -144,6 +174,9 @@ class RoutedExpertsSpec:
     kind: str = "routed_experts"
     scoring: str = "softmax_of_chosen"
     route_scale: float = 1.0
+    activation: str = "silu"
+    limit: Optional[float] = None
+    slope: float = 1.702
 
 
 @dataclass(frozen=True)
@@ -297,6 +330,30 @@ class ChannelDecayScanSpec:
 
 
 @dataclass(frozen=True)
+class ForgetWriteScanSpec:
+    """HGRN2: linear attention whose forget gate also decides what is written.  Per head a matrix state S
+    [key_dim, value_dim]: f = l + (1 - l) sigmoid(f_proj(x) + f_bias) per key channel with a learned lower bound l
+    (``lower`` [n_heads * key_dim]); S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T, o_t = S_t^T q_t with
+    q = silu(q_proj(x)) and v = v_proj(x); there is no key and no other scale.  Each head's o is divided by its root
+    mean square and multiplied by ``out_norm`` [value_dim] (one weight for all heads); the heads go through
+    ``o_proj``.  The gate, its complement and the state are float32."""
+
+    width: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    eps: float
+    q_proj: str
+    f_proj: str
+    f_bias: str
+    lower: str
+    v_proj: str
+    out_norm: str
+    o_proj: str
+    kind: str = "forget_write_scan"
+
+
+@dataclass(frozen=True)
 class ScalarGateScanSpec:
     """The matrix memory of xLSTM: per head a state S [key_dim, value_dim], a vector n and a running maximum m, moved
     by a log input gate i = cap tanh((W_i x + b_i) / cap) and a log forget gate f = logsigmoid(cap tanh((W_f x + b_f) /
@@ -367,6 +424,17 @@ class StreamConnectionSpec:
 
 
 @dataclass(frozen=True)
+class InputConvSpec:
+    """What a sub-layer reads, h (its norm's output), is replaced by h + conv(h): a causal convolution over time on
+    each channel, conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j) with zeros before the sequence's start.  ``weight``
+    names the tensor [width, taps] (no bias).  The last taps - 1 inputs h of a request belong to its state."""
+
+    width: int
+    taps: int
+    weight: str
+
+
+@dataclass(frozen=True)
 class ResidualGateSpec:
     """A sub-layer's result is multiplied element by element by sigmoid(weight h + bias) before it joins the stream,
     h being what the sub-layer itself reads (the norm's output).  ``weight`` [width, width], ``bias`` [width]."""
@@ -394,6 +462,8 @@ class SubLayerSpec:
     connection: Optional[Any] = None
     # for the arrangement that norms after the sum: the norm of the stream itself once the part's output is in it
     sum_norm: Optional[Any] = None
+    # a short convolution over time on what the part reads (InputConvSpec), for arrangements that apply it
+    input_conv: Optional[Any] = None
 
 
 @dataclass(frozen=True)
@@ -436,7 +506,7 @@ class LayerSpec:
             if s.category == category:
                 if seen == index:
                     s = SubLayerSpec(part=part, category=category, norm=s.norm, post_norm=s.post_norm,
-                                     connection=s.connection, sum_norm=s.sum_norm)
+                                     connection=s.connection, sum_norm=s.sum_norm, input_conv=s.input_conv)
                 seen += 1
             subs.append(s)
         if seen <= index:
