@@ -232,8 +232,9 @@ class Attention:
             kernels.mix_queries(q, self.mix, s.n_kv_heads, mixed)
             kernels.joint_attention(mixed, k_pages, v_pages, table, ctx, s.scale, self.span, self.dist_bias, out)
         else:
-            kernels.paged_attention(q, k_pages, v_pages, table, ctx, s.scale, self.span, out,
-                                    head_scale=self.head_scale, slopes=self.slopes, sinks=self.sinks)
+            per_head = {k: t for k, t in (("head_scale", self.head_scale), ("slopes", self.slopes),
+                                          ("sinks", self.sinks)) if t is not None}
+            kernels.paged_attention(q, k_pages, v_pages, table, ctx, s.scale, self.span, out, **per_head)
         if s.gate_proj is not None:          # the heads side by side times sigmoid(gate(x))
             gated = torch.empty_like(out)
             kernels.head_norm_gate(out.view(n, s.n_heads, self.value_dim), qkv[:, self.gate_col:], None, False,

@@ -169,7 +169,8 @@ class HyperConnectionBlock:
 
     def parts(self):
         for s in self.sublayers:
-            yield s.part
+            if s.part is not None:
+                yield s.part
             yield s.norm
 
     def forward(self, ctx, cache_id: int, residual: torch.Tensor, pending):
@@ -177,6 +178,8 @@ class HyperConnectionBlock:
             raise ValueError(f"a hyper-connection block of {self.streams} streams got a residual of shape "
                              f"{tuple(residual.shape)}")
         for s, (read, gain, mix), conv in zip(self.sublayers, self.connections, self.convs):
+            if s.part is None:       # a sub-layer without a part: its tensors are read and nothing runs
+                continue
             h = s.norm.add_norm(residual, pending, read=read)
             if conv is not None:
                 h = conv(ctx, cache_id, h)

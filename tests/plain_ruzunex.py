@@ -132,7 +132,8 @@ def sink_attention(h, m: dict, w: Dict[str, torch.Tensor], p: str, eps: float) -
         q = rotate_half(q, pos, int(rot["dims"]), float(rot["base"]))
         k = rotate_half(k, pos, int(rot["dims"]), float(rot["base"]))
     s = attention_scores(q, k, float(m["scale"])) * w[f"{p}.temp"][:, None, None]
-    prob = sink_softmax(s, visible(T, None), w[f"{p}.sink"])
+    window = int(m["mask"]["size"]) if m.get("mask") else None      # no mask: every earlier position is seen
+    prob = sink_softmax(s, visible(T, window), w[f"{p}.sink"])
     return weighted_values(prob, v.view(T, G, E)) @ w[f"{p}.o"].T
 
 
@@ -227,3 +228,13 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], d
         if layer_sums is not None:
             layer_sums.append(x.sum(dim=1))
     return rms_norm(x.sum(dim=1), w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(config: dict, weights: Dict[str, torch.Tensor], prompt: List[int], n_new: int, dtype=torch.float32) -> List[int]:
+    """The tokens that the largest logit picks, one after the other, the whole sequence run again for each."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(torch.argmax(forward(config, weights, toks, dtype)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
