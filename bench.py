@@ -28,6 +28,14 @@ layer's keys and values; a dense feed-forward and routed experts) beside the Veb
 model (scans with a matrix state beside attention, per-request state slots beside pages), at equal width, heads,
 layers and feed-forward parameters, and its scan beside Vebonex's scans.
 
+    python bench.py --design ruzunex [--design-layers N]
+
+does the same for the Ruzunex design (window attention with a slope per head, blended values and a gate; attention
+behind short convolutions with a sink beside HGRN2; hyper-connections with a convolution in front of every sub-layer;
+a gelu feed-forward and routed experts) beside the Sefalorn design, the closest existing model (two mixers side by
+side, window attention with a distance penalty, a matrix state in slots, routed experts), at equal width, heads,
+layers and feed-forward size, and the design's own kernels each beside the like kernel of the closest model.
+
     python bench.py --design sefalorn [--design-layers N]
 
 does the same for the Sefalorn design (window attention with mixed heads and a distance penalty beside the gated
@@ -250,6 +258,28 @@ def sefalorn_config(width: int, heads: int, ff: int, n_layers: int, vocab: int) 
             "max_positions": 8192, "layers": [layer(i) for i in range(n_layers)]}
 
 
+def ruzunex_config(width: int, heads: int, ff: int, n_layers: int, vocab: int) -> dict:
+    """Layers in the order window attention, window attention, parallel (attention behind short convolutions with a
+    sink, of heads / 2 heads, beside HGRN2 of heads / 2 heads), repeated; a dense feed-forward after the first of
+    three, eight routed experts of ff / 8 (two chosen) after the others; two streams, four taps in front of every
+    sub-layer."""
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 8, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+
+    def layer(i):
+        if i % 3 < 2:
+            return {"type": "attention", "mlp": dense if i % 3 == 0 else moe,
+                    "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                              "mask": {"size": 1024}, "v_mix": True}}
+        left = {"heads": heads // 2, "kv_heads": max(heads // 8, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                "conv": 4, "rot": {"base": 1e6, "dims": 64}}
+        return {"type": "parallel", "mlp": moe,
+                "mixer": {"left": left, "right": {"heads": heads // 2, "dim": 128, "vdim": 128},
+                          "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Ruzunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "streams": 2,
+            "canon": {"taps": 4}, "max_positions": 8192, "layers": [layer(i) for i in range(n_layers)]}
+
+
 def design_bench(args) -> int:
     import argparse as ap_
     import gc
@@ -322,6 +352,55 @@ def design_bench(args) -> int:
         r["frac_bf16"] = round(r["TFLOPs"] / pk["bf16_tflops"], 4)
         return r
 
+    if args.design == "ruzunex":
+        sizes = []
+        for name, width, heads, ff in (("width 2048", 2048, 16, 8192), ("width 4096", 4096, 32, 16384)):
+            n_layers = args.design_layers
+            ours = measure(ruzunex_config(width, heads, ff, n_layers, vocab))
+            closest = measure(sefalorn_config(width, heads, ff, n_layers, vocab))
+            sizes.append({"size": name, "layers": n_layers, "heads": heads, "ff": ff, "ruzunex": ours,
+                          "sefalorn_equal_size": closest})
+        rows = []
+        for heads in (16, 32):
+            half, kv = heads // 2, max(heads // 8, 1)
+            att = dict(impl="mma", context_before=0, splits=0, min_tiles=0, max_context=0, head_dim=128)
+            # the design's kernels, each followed by the like kernel of the closest model at equal sizes
+            rows.append(microbench.scan(ns(mode="forget", groups=0, form="prefill", batch=1, tokens=2048, heads=half,
+                                           key_dim=128, value_dim=128)))
+            rows.append(microbench.scan(ns(mode="delta", groups=0, form="prefill", batch=1, tokens=2048, heads=half,
+                                           key_dim=128, value_dim=128)))
+            for b in (8, 64):
+                rows.append(microbench.scan(ns(mode="forget", groups=0, form="decode", batch=b, tokens=1, heads=half,
+                                               key_dim=128, value_dim=128)))
+                rows.append(microbench.scan(ns(mode="delta", groups=0, form="decode", batch=b, tokens=1, heads=half,
+                                               key_dim=128, value_dim=128)))
+            # the left half of a parallel layer (every earlier key, a factor and a sink per head), the window attention
+            # (a slope per head), the plain kernel they are built on, and the closest model's attention
+            rows.append(microbench.attention(ns(form="prefill", batch=1, context=2048, tokens=2048, window=0,
+                                                per_head=True, heads=half, kv_heads=kv, **att)))
+            rows.append(microbench.attention(ns(form="prefill", batch=1, context=2048, tokens=2048, window=1024,
+                                                per_head=True, heads=heads, kv_heads=heads // 4, **att)))
+            rows.append(microbench.attention(ns(form="prefill", batch=1, context=2048, tokens=2048, window=1024,
+                                                per_head=False, heads=heads, kv_heads=heads // 4, **att)))
+            rows.append(microbench.joint(ns(form="prefill", impl="mma", batch=1, context=2048, tokens=2048, context_before=0,
+                                            window=1024, splits=0, heads=half, kv_heads=kv, head_dim=128)))
+            for b in (8, 64):
+                rows.append(microbench.attention(ns(form="decode", batch=b, context=2048, tokens=1, window=0,
+                                                    per_head=True, heads=half, kv_heads=kv, **att)))
+                rows.append(microbench.attention(ns(form="decode", batch=b, context=2048, tokens=1, window=1024,
+                                                    per_head=True, heads=heads, kv_heads=heads // 4, **att)))
+                rows.append(microbench.attention(ns(form="decode", batch=b, context=2048, tokens=1, window=1024,
+                                                    per_head=False, heads=heads, kv_heads=heads // 4, **att)))
+                rows.append(microbench.joint(ns(form="decode", impl="mma", batch=b, context=2048, tokens=1, context_before=0,
+                                                window=1024, splits=0, heads=half, kv_heads=kv, head_dim=128)))
+            for form, n in (("prefill", 2048), ("decode", 8)):
+                for impl in ("conv", "plain"):
+                    rows.append(microbench.store(ns(form=form, impl=impl, batch=n, context=2048, tokens=n, taps=4,
+                                                    heads=half, kv_heads=kv, head_dim=128)))
+        print(json.dumps({"design": "Ruzunex", "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random weights",
+                          "prompt_len": PROMPT_LEN, "decode_batch": batch, "decode_steps": args.design_steps,
+                          "peaks": pk, "sizes": sizes, "kernels": [fractions(r) for r in rows]}))
+        return 0
     if args.design == "sefalorn":
         sizes = []
         for name, width, heads, ff in (("width 2048", 2048, 16, 8192), ("width 4096", 4096, 32, 16384)):
@@ -426,7 +505,7 @@ def main() -> int:
     ap.add_argument("--clock-interval-ms", type=int, default=200, help="how often nvidia-smi is asked for the clocks")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points and the prefill")
     ap.add_argument("--no-workloads", action="store_true", help="skip the Qwen3-0.6B and Qwen3-32B workloads")
-    ap.add_argument("--design", choices=["vebonex", "tikizen", "sefalorn"],
+    ap.add_argument("--design", choices=["vebonex", "tikizen", "sefalorn", "ruzunex"],
                     help="another workload: this design beside the closest model")
     ap.add_argument("--design-layers", type=int, default=8, help="layers of both models of --design")
     ap.add_argument("--design-steps", type=int, default=64, help="timed decode steps of --design")

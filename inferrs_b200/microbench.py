@@ -101,18 +101,27 @@ def attention(args) -> dict:
     out = torch.empty(n, nh * d, dtype=torch.bfloat16, device=dev)
     table = table.to(dev)
     scale = d ** -0.5
+    window = getattr(args, "window", 0) or None
+    per_head = {}
+    if getattr(args, "per_head", False):       # a factor, a slope and a sink per head (the ``mma.sync`` kernel only)
+        if args.impl != "mma":
+            raise SystemExit("--per-head is an option of --impl mma")
+        per_head = {"head_scale": 1.0 + 0.1 * torch.randn(nh, device=dev),
+                    "slopes": torch.tensor([2.0 ** (-8.0 * (h + 1) / nh) for h in range(nh)], device=dev),
+                    "sinks": torch.randn(nh, device=dev)}
+    seen = lambda n_keys: min(n_keys, window) if window else n_keys      # noqa: E731
     if args.form == "decode":
         if args.impl == "mma":
-            splits = args.splits or kernels.decode_splits(args.batch, nkv, args.context)
+            splits = args.splits or kernels.decode_splits(args.batch, nkv, seen(args.context))
             fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, row_request, q_start, n, q_start,  # noqa: E731
-                                                     positions, scale, None, out, True, splits)
+                                                     positions, scale, window, out, True, splits, **per_head)
         else:
             splits, min_tiles = kernels.decode_slices(args.batch, nkv, args.max_context or args.context)
             splits, min_tiles = args.splits or splits, args.min_tiles or min_tiles
-            fn = lambda: kernels.paged_attention_decode(q, k_pages, v_pages, table, positions, scale, None, out,  # noqa: E731
+            fn = lambda: kernels.paged_attention_decode(q, k_pages, v_pages, table, positions, scale, window, out,  # noqa: E731
                                                         splits, min_tiles=min_tiles)
-        byts = 2 * 2 * sum(lens) * nkv * d
-        flops = 4 * nh * d * sum(lens)
+        byts = 2 * 2 * sum(seen(n_keys) for n_keys in lens) * nkv * d
+        flops = 4 * nh * d * sum(seen(n_keys) for n_keys in lens)
         extra = {"batch": args.batch, "context": args.context, "splits": splits}
     else:
         tpt = kernels.pair_tile_tokens(nh, nkv) if args.impl == "tcgen05-pair" else \
@@ -123,17 +132,21 @@ def attention(args) -> dict:
         tile_row0 = torch.tensor(row0, dtype=torch.int32, device=dev)
         if args.impl == "tcgen05":
             fn = lambda: kernels.paged_attention_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
-                                                         q_start, positions, scale, None, out)
+                                                         q_start, positions, scale, window, out)
         elif args.impl == "tcgen05-pair":
             fn = lambda: kernels.paged_attention_pair_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
-                                                              q_start, positions, scale, None, out)
+                                                              q_start, positions, scale, window, out)
         else:
             fn = lambda: kernels.paged_attention_mma(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
-                                                     q_start, positions, scale, None, out, False)
+                                                     q_start, positions, scale, window, out, False, **per_head)
         byts = 2 * 2 * lens[0] * nkv * d + 2 * 2 * n * nh * d
         t, c = args.tokens, args.context_before
-        flops = 4 * nh * d * (t * c + t * (t + 1) // 2)
+        flops = 4 * nh * d * sum(seen(c + i + 1) for i in range(t))
         extra = {"tokens": args.tokens, "context_before": args.context_before}
+    if window:
+        extra["window"] = window
+    if per_head:
+        extra["per_head"] = "factor, slope, sink"
     us = _time(fn, args.iters)
     return dict({"kernel": f"attention/{args.form}" + (f"/{args.impl}" if args.form == "prefill" else ""), "heads": nh, "kv_heads": nkv, "head_dim": d, "us": round(us, 2),
                  "GBps": round(byts / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1)}, **extra)
@@ -154,10 +167,12 @@ def scan(args) -> dict:
         return _delta_scan(args, lens, dtype)
     ld = 2 * h * d + 2 * h * e
     proj = torch.randn(n, ld, device=dev).to(dtype)
-    mode = kernels.SCAN_CHANNEL_DECAY if args.mode == "decay" else kernels.SCAN_SCALAR_GATES
-    gw = h * d if args.mode == "decay" else 2 * h
+    mode = {"decay": kernels.SCAN_CHANNEL_DECAY, "forget": kernels.SCAN_FORGET_WRITE}.get(args.mode, kernels.SCAN_SCALAR_GATES)
+    gw = h * d if args.mode in ("decay", "forget") else 2 * h
     gates = torch.randn(n, gw, device=dev)
     bias = torch.randn(gw, device=dev) + 3.0
+    if args.mode == "forget":          # the biases and then the lower bounds
+        bias = torch.cat([bias, torch.rand(gw, device=dev)])
     n_state = h * e * d + (h * d + h if args.mode == "gates" else 0)
     state = torch.zeros(len(lens) + 1, n_state, device=dev)
     q_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
@@ -172,6 +187,56 @@ def scan(args) -> dict:
     return {"kernel": f"scan/{args.mode}/{args.form}", "heads": h, "key_dim": d, "value_dim": e, "rows": n,
             "requests": len(lens), "us": round(us, 2), "GBps": round(byts / us / 1e3, 1),
             "TFLOPs": round(flops / us / 1e6, 2), "us_per_token": round(us / max(lens), 4)}
+
+
+def store(args) -> dict:
+    """What stands between the q | k | v projection and the attention kernel, alone: the kernel that norms per head,
+    turns and stores (``--impl plain``), or the one that also convolves over the last ``--taps`` rows and norms over
+    the whole projection (``--impl conv``).  ``--tokens`` rows of one request, or ``--batch`` requests of one row
+    each.  Bytes: the projection read once (``taps`` times by the convolution, from L2), q, k and v written once."""
+    nh, nkv, d, ps = args.heads, args.kv_heads, args.head_dim, args.page_size
+    dev = torch.device("cuda")
+    lens = [args.tokens] if args.form == "prefill" else [1] * args.batch
+    n = sum(lens)
+    start = 0 if args.form == "prefill" else args.context
+    pages_per = [(start + t + ps - 1) // ps for t in lens]
+    table = torch.full((len(lens), max(pages_per)), -1, dtype=torch.int32)
+    perm, at = torch.randperm(sum(pages_per)).to(torch.int32), 0
+    for r, k in enumerate(pages_per):
+        table[r, :k] = perm[at:at + k]
+        at += k
+    table = table.to(dev)
+    positions = torch.tensor([p for t in lens for p in range(start, start + t)], dtype=torch.int32, device=dev)
+    row_request = torch.tensor([r for r, t in enumerate(lens) for _ in range(t)], dtype=torch.int32, device=dev)
+    q_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    slots = torch.arange(len(lens), dtype=torch.int32, device=dev)
+    channels = (nh + 2 * nkv) * d
+    proj = torch.randn(n, channels, device=dev).to(torch.bfloat16)
+    k_pages = torch.zeros(sum(pages_per), nkv, ps, d, device=dev, dtype=torch.bfloat16)
+    v_pages = torch.zeros_like(k_pages)
+    q = torch.empty(n, nh, d, device=dev, dtype=torch.bfloat16)
+    half = d // 2
+    ang = torch.arange(start + max(lens), dtype=torch.float32, device=dev)[:, None] * \
+        (1e4 ** (-torch.arange(half, dtype=torch.float32, device=dev) / half))[None, :]
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    if args.impl == "conv":
+        conv = torch.randn(channels, args.taps, device=dev)
+        state = torch.zeros(len(lens) + 1, (args.taps - 1) * channels, device=dev)
+        wq, wk = torch.ones(nh * d, device=dev, dtype=torch.bfloat16), torch.ones(nkv * d, device=dev, dtype=torch.bfloat16)
+
+        def fn():
+            kernels.conv_norm_rope_store(proj, nh, nkv, d, conv, state, 0, q_start, slots, row_request,
+                                         kernels.NORM_WHOLE, wq, wk, 1e-5, cos, sin, d, positions, table, k_pages,
+                                         v_pages, q)
+            kernels.conv_state_shift(proj, 0, channels, args.taps, state, 0, q_start, slots, len(lens))
+    else:
+        w = torch.ones(d, device=dev, dtype=torch.bfloat16)
+        fn = lambda: kernels.qk_norm_rope_store(proj, nh, nkv, d, True, w, w, 1e-5, cos, sin, d, positions,      # noqa: E731
+                                                row_request, table, k_pages, v_pages, q)
+    us = _time(fn, args.iters)
+    byts = 2 * n * channels * 2
+    return {"kernel": f"store/{args.form}/{args.impl}", "heads": nh, "kv_heads": nkv, "head_dim": d, "rows": n,
+            "us": round(us, 2), "GBps": round(byts / us / 1e3, 1), "TFLOPs": 0.0}
 
 
 def _scalar_decay_scan(args, lens, dtype) -> dict:
@@ -630,6 +695,8 @@ def main(argv=None) -> int:
     a.add_argument("--splits", type=int, default=0)
     a.add_argument("--min-tiles", type=int, default=0, help="decode form: fewest 64-key tiles per slice (0: as the engine chooses)")
     a.add_argument("--max-context", type=int, default=0, help="decode form: the context that the grid is sized for")
+    a.add_argument("--window", type=int, default=0, help="a sliding window of that many keys (0: every earlier key)")
+    a.add_argument("--per-head", action="store_true", help="mma: a factor, a slope and a sink per head on the scores")
     a.add_argument("--heads", type=int, default=32)
     a.add_argument("--kv-heads", type=int, default=8)
     a.add_argument("--head-dim", type=int, default=128)
@@ -637,7 +704,7 @@ def main(argv=None) -> int:
     a.add_argument("--iters", type=int, default=20)
     a.set_defaults(fn=attention)
     sc = sub.add_parser("scan")
-    sc.add_argument("--mode", choices=["decay", "gates", "scalar", "delta"], default="gates",
+    sc.add_argument("--mode", choices=["decay", "gates", "scalar", "delta", "forget"], default="gates",
                     help="a decay per key channel, scalar gates with a running maximum, or one decay per token and head")
     sc.add_argument("--groups", type=int, default=0, help="scalar: groups of heads that share q and k (0: every head its own)")
     sc.add_argument("--form", choices=["decode", "prefill"], default="prefill")
@@ -649,6 +716,20 @@ def main(argv=None) -> int:
     sc.add_argument("--value-dim", type=int, default=128)
     sc.add_argument("--iters", type=int, default=20)
     sc.set_defaults(fn=scan)
+    so = sub.add_parser("store")
+    so.add_argument("--form", choices=["decode", "prefill"], default="prefill")
+    so.add_argument("--impl", choices=["plain", "conv"], default="conv")
+    so.add_argument("--batch", type=int, default=8)
+    so.add_argument("--context", type=int, default=2048)
+    so.add_argument("--tokens", type=int, default=2048)
+    so.add_argument("--taps", type=int, default=4)
+    so.add_argument("--heads", type=int, default=8)
+    so.add_argument("--kv-heads", type=int, default=2)
+    so.add_argument("--head-dim", type=int, default=128)
+    so.add_argument("--page-size", type=int, default=16)
+    so.add_argument("--iters", type=int, default=20)
+    so.set_defaults(fn=store)
+
     jo = sub.add_parser("joint")
     jo.add_argument("--form", choices=["decode", "prefill"], default="prefill")
     jo.add_argument("--impl", choices=["mma", "generic"], default="mma")
