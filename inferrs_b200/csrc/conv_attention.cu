@@ -15,21 +15,23 @@
 
 // ---------------------------------------------------------------------------
 // out[r, c] = add_input * x[r, col + c] + sum_j w[c, j] * input(r - (taps - 1 - j), c), c < C.  w [C, taps] float, the
-// last tap weighs the row itself.
+// last tap weighs the row itself.  shift_single (only for steps in which every request brings exactly one row): the
+// kernel also moves the kept inputs on by one place, so the state is ready for the next step.
 // ---------------------------------------------------------------------------
 __global__ void causal_conv_rows_kernel(const act_t* __restrict__ x, long ld, int col, int C, int taps,
-                                        const float* __restrict__ w, const float* __restrict__ state, long slot_stride,
+                                        const float* __restrict__ w, float* __restrict__ state, long slot_stride,
                                         long state_off, const int* __restrict__ q_start, const int* __restrict__ slots,
                                         const int* __restrict__ row_request, act_t* __restrict__ out, long out_ld,
-                                        int add_input) {
+                                        int add_input, int shift_single) {
     ib_grid_dependency_sync();
     const int row = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     const int req = row_request[row];
     const int row0 = q_start[req];
-    const float* kept = state + (long)slots[req] * slot_stride + state_off;
-    float acc = add_input ? ib_to_float(x[(long)row * ld + col + c]) : 0.0f;
+    float* kept = taps > 1 ? state + (long)slots[req] * slot_stride + state_off : nullptr;
+    const float own = ib_to_float(x[(long)row * ld + col + c]);
+    float acc = add_input ? own : 0.0f;
     for (int j = 0; j < taps; ++j) {
         const int t = row - (taps - 1 - j);
         float v;
@@ -38,12 +40,18 @@ __global__ void causal_conv_rows_kernel(const act_t* __restrict__ x, long ld, in
         acc = fmaf(w[(long)c * taps + j], v, acc);
     }
     out[(long)row * out_ld + c] = ib_from_float<act_t>(acc);
+    // a step in which every request brings one row: the thread that has read the channel's kept inputs moves them
+    // on by one place itself, and no kernel of its own has to follow
+    if (shift_single && taps > 1) {
+        for (int k = 0; k + 1 < taps - 1; ++k) kept[(long)k * C + c] = kept[(long)(k + 1) * C + c];
+        kept[(long)(taps - 2) * C + c] = own;
+    }
 }
 
 IB_EXPORT int ib_causal_conv_rows(const void* x, long ld, int col, int C, int taps, const float* w, const float* state,
                                   long slot_stride, long state_off, const int* q_start, const int* slots,
-                                  const int* row_request, void* out, long out_ld, int add_input, int n_rows,
-                                  cudaStream_t stream) {
+                                  const int* row_request, void* out, long out_ld, int add_input, int shift_single,
+                                  int n_rows, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (C <= 0 || taps <= 0 || x == nullptr || w == nullptr || out == nullptr || col < 0 || ld < col + C || out_ld < C ||
         (taps > 1 && (state == nullptr || slot_stride < state_off + (long)(taps - 1) * C)))
@@ -51,68 +59,104 @@ IB_EXPORT int ib_causal_conv_rows(const void* x, long ld, int col, int C, int ta
     if (n_rows > 65535) return IB_ERR_UNSUPPORTED;
     const int threads = C >= 256 ? 256 : ((C + 31) / 32) * 32;
     ib_launch(causal_conv_rows_kernel, dim3((C + threads - 1) / threads, n_rows), threads, 0, stream, (const act_t*)x,
-              ld, col, C, taps, w, state, slot_stride, state_off, q_start, slots, row_request, (act_t*)out, out_ld,
-              add_input);
+              ld, col, C, taps, w, (float*)state, slot_stride, state_off, q_start, slots, row_request, (act_t*)out, out_ld,
+              add_input, shift_single);
     return ib_launch_status();
 }
 
 // ---------------------------------------------------------------------------
 // One block per row of a fused projection q | k | v (H heads of D, G heads of D, G heads of E, from column 0 on):
-//   1. taps > 0: every channel goes through its causal convolution (conv_w [Cq + Ck + Cv, taps], no bias);
+//   1. taps > 0: every channel goes through its causal convolution (conv_w [taps, Cq + Ck + Cv]: tap-major, so that
+//      neighbouring channels' weights are neighbours; no bias);
 //   2. norm_mode 1: every head of q and of k is divided by its root mean square over D and multiplied by the
 //      weight [D]; norm_mode 2: all of q (all of k) is divided by one root mean square over its H * D (G * D)
 //      numbers and multiplied by the weight [H * D] ([G * D]); 0: neither;
 //   3. the first rot_dim numbers of every head of q and k turn by the row's position (i with i + rot_dim / 2);
 //   4. q goes to q_out [rows, H, D], k and v to their pages at the row's position.  A request's last row of the step
 //      clears the places behind its value in the value's page (see the kernel that stores without a convolution).
-// The row lives in shared memory as floats between the steps.
+// The row lives in shared memory as floats between the steps.  VEC: sixteen bytes per thread and access (eight
+// bfloat16 or four floats), for head sizes that are multiples of that many elements and aligned tensors.
+// shift_single (only for steps in which every request brings exactly one row): the kernel also moves the kept inputs
+// on by one place, so that no kernel of its own has to follow.
 // ---------------------------------------------------------------------------
-template <typename WT>
+#define CN_VEC (16 / (int)sizeof(act_t))
+struct alignas(16) CnActVec { act_t v[CN_VEC]; };
+
+template <typename WT, bool VEC>
 __global__ void conv_norm_rope_store_kernel(
     const act_t* __restrict__ proj, long ld, int H, int G, int D, int E, int taps, const float* __restrict__ conv_w,
-    const float* __restrict__ state, long slot_stride, long state_off, const int* __restrict__ q_start,
+    float* __restrict__ state, long slot_stride, long state_off, const int* __restrict__ q_start,
     const int* __restrict__ slots, const int* __restrict__ row_request, int norm_mode, const WT* __restrict__ q_weight,
     const WT* __restrict__ k_weight, float eps, const float* __restrict__ cos_table, const float* __restrict__ sin_table,
     int rot_dim, int table_rows, const int* __restrict__ positions, const int* __restrict__ block_table, int max_pages,
-    int page_size, int n_pages, act_t* __restrict__ k_pages, act_t* __restrict__ v_pages, act_t* __restrict__ q_out) {
-    extern __shared__ float cn_row[];
+    int page_size, int n_pages, act_t* __restrict__ k_pages, act_t* __restrict__ v_pages, act_t* __restrict__ q_out,
+    int shift_single) {
+    extern __shared__ __align__(16) float cn_row[];
     __shared__ float red[32];
     ib_grid_dependency_sync();
+    constexpr int V = VEC ? CN_VEC : 1;
     const int row = blockIdx.x;
     const int Cq = H * D, Ck = G * D, Cv = G * E, C = Cq + Ck + Cv;
     const int pos = positions[row];
     if (pos < 0 || (rot_dim > 0 && pos >= table_rows)) return;      // outside the tables: the row is left out
     const int req = row_request[row];
     const int row0 = q_start[req];
-    const float* kept = state ? state + (long)slots[req] * slot_stride + state_off : nullptr;
+    float* kept = (state && taps > 1) ? state + (long)slots[req] * slot_stride + state_off : nullptr;
 
     // 1. the convolution (or the projection as it is)
     float ssq = 0.0f, ssk = 0.0f;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float acc;
-        if (taps > 0) {
-            acc = 0.0f;
-            for (int j = 0; j < taps; ++j) {
-                const int t = row - (taps - 1 - j);
-                float v;
-                if (t >= row0) v = ib_to_float(proj[(long)t * ld + c]);
-                else v = kept[(long)(taps - 1 - (row0 - t)) * C + c];
-                acc = fmaf(conv_w[(long)c * taps + j], v, acc);
+    for (int c0 = threadIdx.x * V; c0 < C; c0 += blockDim.x * V) {
+        float acc[V], own[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = 0.0f;
+        const int n_taps = taps > 0 ? taps : 1;
+        for (int j = 0; j < n_taps; ++j) {
+            const int t = row - (n_taps - 1 - j);
+            float v[V];
+            if (t >= row0) {
+                if (VEC) {
+                    const CnActVec a = *reinterpret_cast<const CnActVec*>(proj + (long)t * ld + c0);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) v[i] = ib_to_float(a.v[i]);
+                } else {
+                    v[0] = ib_to_float(proj[(long)t * ld + c0]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < V; ++i) v[i] = kept[(long)(n_taps - 1 - (row0 - t)) * C + c0 + i];
             }
-        } else {
-            acc = ib_to_float(proj[(long)row * ld + c]);
+            if (j == n_taps - 1) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) own[i] = v[i];
+            }
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = taps > 0 ? fmaf(conv_w[(long)j * C + c0 + i], v[i], acc[i]) : v[i];
         }
-        cn_row[c] = acc;
-        if (c < Cq) ssq += acc * acc;
-        else if (c < Cq + Ck) ssk += acc * acc;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            cn_row[c0 + i] = acc[i];
+            if (c0 + i < Cq) ssq += acc[i] * acc[i];
+            else if (c0 + i < Cq + Ck) ssk += acc[i] * acc[i];
+        }
+        if (shift_single && kept != nullptr) {        // this thread alone has read these channels' kept inputs
+            for (int k = 0; k + 1 < taps - 1; ++k)
+#pragma unroll
+                for (int i = 0; i < V; ++i) kept[(long)k * C + c0 + i] = kept[(long)(k + 1) * C + c0 + i];
+#pragma unroll
+            for (int i = 0; i < V; ++i) kept[(long)(taps - 2) * C + c0 + i] = own[i];
+        }
     }
     // 2. the norms
     if (norm_mode == 2) {
         ssq = ib_block_sum(ssq, red);
         ssk = ib_block_sum(ssk, red);
         const float inv_q = 1.0f / sqrtf(ssq / (float)Cq + eps), inv_k = 1.0f / sqrtf(ssk / (float)Ck + eps);
-        for (int c = threadIdx.x; c < Cq + Ck; c += blockDim.x)      // the thread that wrote the place reads it
-            cn_row[c] *= c < Cq ? inv_q * ib_to_float(q_weight[c]) : inv_k * ib_to_float(k_weight[c - Cq]);
+        for (int c0 = threadIdx.x * V; c0 < Cq + Ck; c0 += blockDim.x * V)      // the thread that wrote the places reads them
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const int c = c0 + i;
+                cn_row[c] *= c < Cq ? inv_q * ib_to_float(q_weight[c]) : inv_k * ib_to_float(k_weight[c - Cq]);
+            }
         __syncthreads();
     } else if (norm_mode == 1) {
         __syncthreads();
@@ -139,34 +183,49 @@ __global__ void conv_norm_rope_store_kernel(
     const int half = rot_dim / 2;
     const float* cs = rot_dim > 0 ? cos_table + (long)pos * half : nullptr;
     const float* sn = rot_dim > 0 ? sin_table + (long)pos * half : nullptr;
-    for (int c = threadIdx.x; c < Cq + Ck; c += blockDim.x) {
-        const int head = c / D, j = c - head * D;
-        float o = cn_row[c];
-        if (j < half) o = o * cs[j] - cn_row[c + half] * sn[j];
-        else if (j < rot_dim) o = cn_row[c - half] * sn[j - half] + o * cs[j - half];
-        if (head < H) q_out[((long)row * H + head) * D + j] = ib_from_float<act_t>(o);
-        else if (kv_place >= 0) k_pages[(kv_place + (long)(head - H) * page_size) * D + j] = ib_from_float<act_t>(o);
+    for (int c0 = threadIdx.x * V; c0 < Cq + Ck; c0 += blockDim.x * V) {
+        const int head = c0 / D, j0 = c0 - head * D;      // a thread's V numbers lie in one head
+        CnActVec o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int c = c0 + i, j = j0 + i;
+            float r = cn_row[c];
+            if (j < half) r = r * cs[j] - cn_row[c + half] * sn[j];
+            else if (j < rot_dim) r = cn_row[c - half] * sn[j - half] + r * cs[j - half];
+            o.v[i] = ib_from_float<act_t>(r);
+        }
+        act_t* dst = head < H ? q_out + ((long)row * H + head) * D + j0
+                              : (kv_place >= 0 ? k_pages + (kv_place + (long)(head - H) * page_size) * D + j0 : nullptr);
+        if (dst == nullptr) continue;
+        if (VEC) *reinterpret_cast<CnActVec*>(dst) = o; else dst[0] = o.v[0];
     }
     if (kv_place < 0) return;
+    for (int c0 = threadIdx.x * V; c0 < Cv; c0 += blockDim.x * V) {
+        const int g = c0 / E, j0 = c0 - g * E;
+        CnActVec o;
+#pragma unroll
+        for (int i = 0; i < V; ++i) o.v[i] = ib_from_float<act_t>(cn_row[Cq + Ck + c0 + i]);
+        act_t* dst = v_pages + (kv_place + (long)g * page_size) * E + j0;
+        if (VEC) *reinterpret_cast<CnActVec*>(dst) = o; else dst[0] = o.v[0];
+    }
     const bool last = row + 1 >= (int)gridDim.x || row_request[row + 1] != req;
     const int behind = last ? (page_size - 1 - pos % page_size) * E : 0;
-    for (int c = threadIdx.x; c < Cv; c += blockDim.x) {
-        const int g = c / E, j = c - g * E;
-        v_pages[(kv_place + (long)g * page_size) * E + j] = ib_from_float<act_t>(cn_row[Cq + Ck + c]);
-    }
-    for (int g = 0; g < G; ++g) {
+    for (int g = 0; g < G && behind > 0; ++g) {
         act_t* dst = v_pages + (kv_place + (long)g * page_size) * E + E;
         for (int j = threadIdx.x; j < behind; j += blockDim.x) dst[j] = ib_from_float<act_t>(0.0f);
     }
 }
 
+static inline bool cn_aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
 IB_EXPORT int ib_conv_norm_rope_store(const void* proj, long ld, int n_rows, int H, int G, int D, int E, int taps,
-                                      const float* conv_w, const float* state, long slot_stride, long state_off,
+                                      const float* conv_w, float* state, long slot_stride, long state_off,
                                       const int* q_start, const int* slots, const int* row_request, int norm_mode,
                                       const void* q_weight, const void* k_weight, int weight_is_f32, float eps,
                                       const float* cos_table, const float* sin_table, int rot_dim, int table_rows,
                                       const int* positions, const int* block_table, int max_pages, int page_size,
-                                      int n_pages, void* k_pages, void* v_pages, void* q_out, cudaStream_t stream) {
+                                      int n_pages, void* k_pages, void* v_pages, void* q_out, int shift_single,
+                                      cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (H <= 0 || G <= 0 || D <= 0 || E <= 0 || taps < 0 || rot_dim < 0 || rot_dim > D || (rot_dim & 1) ||
         norm_mode < 0 || norm_mode > 2 || page_size <= 0 || max_pages <= 0 || proj == nullptr || q_out == nullptr ||
@@ -180,20 +239,28 @@ IB_EXPORT int ib_conv_norm_rope_store(const void* proj, long ld, int n_rows, int
     if (rot_dim > 0 && (cos_table == nullptr || sin_table == nullptr || table_rows <= 0)) return IB_ERR_ARGUMENT;
     const size_t smem = (size_t)C * sizeof(float);
     if (smem > 200 * 1024) return IB_ERR_UNSUPPORTED;
-    static IbDeviceSet set_f, set_b;
-    const int threads = C >= 2048 ? 512 : 256;
-#define IB_CNRS(WT, SET)                                                                                              \
+    static IbDeviceSet sets[4];
+    const bool vec = D % CN_VEC == 0 && E % CN_VEC == 0 && ld % CN_VEC == 0 && cn_aligned16(proj) &&
+                     cn_aligned16(q_out) && cn_aligned16(k_pages) && cn_aligned16(v_pages);
+    const long units = vec ? C / CN_VEC : C;
+    const int threads = units >= 512 ? 512 : (units >= 256 ? 256 : (units > 64 ? 128 : 64));
+#define IB_CNRS(WT, VEC, SET)                                                                                         \
     do {                                                                                                              \
         if (smem > 48 * 1024) {                                                                                       \
-            const int e = ib_allow_dynamic_smem(SET, conv_norm_rope_store_kernel<WT>, 200 * 1024);                    \
+            const int e = ib_allow_dynamic_smem(sets[SET], conv_norm_rope_store_kernel<WT, VEC>, 200 * 1024);         \
             if (e != IB_OK) return e;                                                                                 \
         }                                                                                                             \
-        ib_launch(conv_norm_rope_store_kernel<WT>, n_rows, threads, smem, stream, (const act_t*)proj, ld, H, G, D, E, \
-                  taps, conv_w, state, slot_stride, state_off, q_start, slots, row_request, norm_mode,                \
+        ib_launch(conv_norm_rope_store_kernel<WT, VEC>, n_rows, threads, smem, stream, (const act_t*)proj, ld, H, G,  \
+                  D, E, taps, conv_w, state, slot_stride, state_off, q_start, slots, row_request, norm_mode,          \
                   (const WT*)q_weight, (const WT*)k_weight, eps, cos_table, sin_table, rot_dim, table_rows, positions, \
-                  block_table, max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out);       \
+                  block_table, max_pages, page_size, n_pages, (act_t*)k_pages, (act_t*)v_pages, (act_t*)q_out,        \
+                  shift_single);                                                                                      \
     } while (0)
-    if (weight_is_f32) IB_CNRS(float, set_f); else IB_CNRS(__nv_bfloat16, set_b);
+    if (weight_is_f32) {
+        if (vec) IB_CNRS(float, true, 0); else IB_CNRS(float, false, 1);
+    } else {
+        if (vec) IB_CNRS(__nv_bfloat16, true, 2); else IB_CNRS(__nv_bfloat16, false, 3);
+    }
 #undef IB_CNRS
     return ib_launch_status();
 }

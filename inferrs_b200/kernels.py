@@ -109,11 +109,11 @@ _SIGNATURES = {
     "ib_decay_scan": [c_void_p, c_long, c_int, c_int, c_int, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p,
                       c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ib_causal_conv_rows": [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_long, c_long, c_void_p, c_void_p,
-                            c_void_p, c_void_p, c_long, c_int, c_int, c_void_p],
+                            c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_void_p],
     "ib_conv_norm_rope_store": [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_long,
                                 c_long, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p,
                                 c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
-                                c_void_p, c_void_p],
+                                c_void_p, c_int, c_void_p],
     "ib_blend_columns": [c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_void_p, c_int, c_void_p],
     "ib_sample": [c_void_p, c_long, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_int, c_void_p, c_void_p],
@@ -1033,13 +1033,15 @@ def conv_state_shift(proj: torch.Tensor, conv_col: int, channels: int, taps: int
 
 def causal_conv_rows(x: torch.Tensor, col: int, conv_w: torch.Tensor, state: Optional[torch.Tensor], state_off: int,
                      q_start: torch.Tensor, slots: torch.Tensor, row_request: torch.Tensor, out: torch.Tensor,
-                     add_input: bool):
+                     add_input: bool, shift_single: bool = False):
     """out[r, c] = (x[r, col + c] if ``add_input``) + sum_j conv_w[c, j] * input(r - (taps - 1 - j), c) for the
     channels c < C = conv_w.shape[0]: a causal convolution per channel over a request's rows, the last tap weighing
     the row itself.  input(t, c) is this step's row t of the same request, or what the request's slot of ``state``
     keeps from earlier steps: its last taps - 1 inputs, oldest first, [taps - 1, C] float32 from ``state_off`` on
     (:func:`conv_state_shift` writes them after the step; zeros for a new request).  ``x`` is a [rows, ld] view in
-    the activation dtype with unit last stride; ``out`` [rows, C]."""
+    the activation dtype with unit last stride; ``out`` [rows, C].  ``shift_single``, only for steps in which every
+    request brings exactly one row: the kernel moves the kept inputs on itself and no :func:`conv_state_shift`
+    follows."""
     act = out.dtype
     _need(conv_w, "conv_w", (torch.float32,), 2)
     _need(out, "out", _W, 2)
@@ -1057,8 +1059,8 @@ def causal_conv_rows(x: torch.Tensor, col: int, conv_w: torch.Tensor, state: Opt
                           f"{tuple(out.shape)}")
     _check(_core(act).ib_causal_conv_rows(
         _p(x), x.stride(0), int(col), channels, taps, _p(conv_w), _p(state), 0 if state is None else state[0].numel(),
-        int(state_off), _p(q_start), _p(slots), _p(row_request), _p(out), out.stride(0), int(bool(add_input)), n,
-        _stream()), "causal_conv_rows")
+        int(state_off), _p(q_start), _p(slots), _p(row_request), _p(out), out.stride(0), int(bool(add_input)),
+        int(bool(shift_single)), n, _stream()), "causal_conv_rows")
 
 
 NORM_NONE, NORM_PER_HEAD, NORM_WHOLE = 0, 1, 2
@@ -1069,10 +1071,11 @@ def conv_norm_rope_store(proj: torch.Tensor, n_heads: int, n_kv_heads: int, head
                          q_start: torch.Tensor, slots: torch.Tensor, row_request: torch.Tensor, norm_mode: int,
                          q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                          cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot_dim: int, positions: torch.Tensor,
-                         block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, q_out: torch.Tensor):
+                         block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, q_out: torch.Tensor,
+                         shift_single: bool = False):
     """One pass over the first columns q | k | v of ``proj`` [rows, ld] (H heads of D, G heads of D, G heads of E):
-    a causal convolution per channel (``conv_w`` [channels, taps], None: none; earlier steps' inputs from ``state``
-    as in :func:`causal_conv_rows`), then the norms (NORM_PER_HEAD: every head of q and k divided by its root mean
+    a causal convolution per channel (``conv_w`` [taps, channels], tap-major, the last tap weighing the row itself;
+    None: none; earlier steps' inputs from ``state`` as in :func:`causal_conv_rows`, ``shift_single`` likewise), then the norms (NORM_PER_HEAD: every head of q and k divided by its root mean
     square, weights [D] or None; NORM_WHOLE: all of q, and all of k, divided by one root mean square over the whole
     projection, weights [H * D] and [G * D]), then the rotation of every head's first ``rot_dim`` numbers by position
     (i with i + rot_dim / 2); q goes to ``q_out`` [rows, H, D], k and v into their pages."""
@@ -1091,9 +1094,9 @@ def conv_norm_rope_store(proj: torch.Tensor, n_heads: int, n_kv_heads: int, head
     n_pages, nkv, page_size, d = k_pages.shape
     v_dim = v_pages.shape[3]
     channels = n_heads * head_dim + n_kv_heads * (head_dim + v_dim)
-    taps = 0 if conv_w is None else conv_w.shape[1]
+    taps = 0 if conv_w is None else conv_w.shape[0]
     if (nkv, d) != (n_kv_heads, head_dim) or v_pages.shape[:3] != k_pages.shape[:3] or proj.shape[1] < channels \
-            or q_out.shape != (n, n_heads, head_dim) or (conv_w is not None and conv_w.shape[0] != channels) \
+            or q_out.shape != (n, n_heads, head_dim) or (conv_w is not None and conv_w.shape[1] != channels) \
             or (taps > 1 and state is None) or positions.shape[0] != n or row_request.shape[0] != n:
         raise KernelError(f"conv_norm_rope_store: proj {tuple(proj.shape)}, pages {tuple(k_pages.shape)} / "
                           f"{tuple(v_pages.shape)}, q_out {tuple(q_out.shape)}, "
@@ -1123,8 +1126,8 @@ def conv_norm_rope_store(proj: torch.Tensor, n_heads: int, n_kv_heads: int, head
         0 if state is None else state[0].numel(), int(state_off), _p(q_start), _p(slots), _p(row_request),
         int(norm_mode), _p(q_weight), _p(k_weight), int(wdt == torch.float32), float(eps),
         _p(cos) if rot_dim else None, _p(sin) if rot_dim else None, int(rot_dim), table_rows, _p(positions),
-        _p(block_table), block_table.shape[1], page_size, n_pages, _p(k_pages), _p(v_pages), _p(q_out), _stream()),
-        "conv_norm_rope_store")
+        _p(block_table), block_table.shape[1], page_size, n_pages, _p(k_pages), _p(v_pages), _p(q_out),
+        int(bool(shift_single)), _stream()), "conv_norm_rope_store")
 
 
 def blend_columns(x: torch.Tensor, col: int, other: torch.Tensor, weight: torch.Tensor):

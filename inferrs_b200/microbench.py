@@ -220,15 +220,16 @@ def store(args) -> dict:
         (1e4 ** (-torch.arange(half, dtype=torch.float32, device=dev) / half))[None, :]
     cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
     if args.impl == "conv":
-        conv = torch.randn(channels, args.taps, device=dev)
+        conv = torch.randn(args.taps, channels, device=dev)
         state = torch.zeros(len(lens) + 1, (args.taps - 1) * channels, device=dev)
         wq, wk = torch.ones(nh * d, device=dev, dtype=torch.bfloat16), torch.ones(nkv * d, device=dev, dtype=torch.bfloat16)
 
         def fn():
             kernels.conv_norm_rope_store(proj, nh, nkv, d, conv, state, 0, q_start, slots, row_request,
                                          kernels.NORM_WHOLE, wq, wk, 1e-5, cos, sin, d, positions, table, k_pages,
-                                         v_pages, q)
-            kernels.conv_state_shift(proj, 0, channels, args.taps, state, 0, q_start, slots, len(lens))
+                                         v_pages, q, shift_single=max(lens) == 1)
+            if max(lens) > 1:
+                kernels.conv_state_shift(proj, 0, channels, args.taps, state, 0, q_start, slots, len(lens))
     else:
         w = torch.ones(d, device=dev, dtype=torch.bfloat16)
         fn = lambda: kernels.qk_norm_rope_store(proj, nh, nkv, d, True, w, w, 1e-5, cos, sin, d, positions,      # noqa: E731

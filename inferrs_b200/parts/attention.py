@@ -133,7 +133,9 @@ class Attention:
         self.sinks = None if spec.sink is None else f32(spec.sink)
         self.slopes = None if spec.distance_slopes is None else \
             torch.tensor([float(a) for a in spec.distance_slopes], dtype=torch.float64).to(torch.float32).to(rt.device)
-        self.conv = None if spec.qkv_conv is None else torch.cat([f32(n) for n in spec.qkv_conv], dim=0).contiguous()
+        # the three convolutions' weights side by side, tap-major [taps, channels] as the kernel reads them
+        self.conv = None if spec.qkv_conv is None else \
+            torch.cat([f32(n) for n in spec.qkv_conv], dim=0).t().contiguous()
         self.blend_weight = None if spec.value_blend is None else f32(spec.value_blend[1]).reshape(1)
         self.o = Linear(weights[spec.o_proj], rt, bias=None if spec.o_bias is None else weights[spec.o_bias])
         # scores penalised by distance and mixed across heads: the mixing is linear, so it is done on the queries
@@ -215,10 +217,12 @@ class Attention:
             state = ctx.storage.side_state(cache_id, s) if taps > 1 else None
             mode = kernels.NORM_WHOLE if s.norm_whole else \
                 (kernels.NORM_PER_HEAD if (s.q_norm is not None or s.k_norm is not None) else kernels.NORM_NONE)
+            single = ctx.max_q_len == 1      # every request brings one row: the kernel moves the kept rows on itself
             kernels.conv_norm_rope_store(qkv, s.n_heads, s.n_kv_heads, s.head_dim, self.conv, state, 0, ctx.q_start,
                                          ctx.slots, ctx.row_request, mode, self.q_weight, self.k_weight, self.eps,
-                                         self.cos, self.sin, self.rot_dim, ctx.positions, table, k_pages, v_pages, q)
-            if state is not None:
+                                         self.cos, self.sin, self.rot_dim, ctx.positions, table, k_pages, v_pages, q,
+                                         shift_single=single)
+            if state is not None and not single:
                 kernels.conv_state_shift(qkv, 0, self.gate_col, taps, state, 0, ctx.q_start, ctx.slots, ctx.n_requests)
         else:
             kernels.qk_norm_rope_store(qkv, s.n_heads, s.n_kv_heads, s.head_dim, s.own_kv, self.q_weight, self.k_weight,

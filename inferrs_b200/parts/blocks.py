@@ -109,8 +109,10 @@ class InputConv:
         s = self.spec
         state = ctx.storage.side_state(cache_id, s) if s.taps > 1 else None
         out = torch.empty_like(h)
-        kernels.causal_conv_rows(h, 0, self.weight, state, 0, ctx.q_start, ctx.slots, ctx.row_request, out, True)
-        if state is not None:
+        single = ctx.max_q_len == 1          # every request brings one row: the kernel moves the kept rows on itself
+        kernels.causal_conv_rows(h, 0, self.weight, state, 0, ctx.q_start, ctx.slots, ctx.row_request, out, True,
+                                 shift_single=single)
+        if state is not None and not single:
             kernels.conv_state_shift(h, 0, s.width, s.taps, state, 0, ctx.q_start, ctx.slots, ctx.n_requests)
         return out
 

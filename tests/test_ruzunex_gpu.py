@@ -565,7 +565,7 @@ def test_convolution_norm_rotation_and_store(H, G, D, E, taps, rot, mode, dtype)
         rows = act(torch.cat([t[:first[r]] if step == 0 else t[first[r]:] for r, t in enumerate(x)]), dtype)
         positions = [p for r in range(2) for p in (range(first[r]) if step == 0 else range(first[r], first[r] + second[r]))]
         q_out = torch.empty(rows.shape[0], H, D, dtype=dtype, device="cuda")
-        kernels.conv_norm_rope_store(rows, H, G, D, conv.cuda().contiguous() if taps else None,
+        kernels.conv_norm_rope_store(rows, H, G, D, conv.t().cuda().contiguous() if taps else None,
                                      state if taps > 1 else None, 0, dev(q_start), slots, dev(row_request), mode,
                                      act(wq, dtype) if mode else None, act(wk, dtype) if mode else None, eps,
                                      cos if rot else None, sin if rot else None, rot, dev(positions), table, k_pages,
@@ -587,6 +587,34 @@ def test_convolution_norm_rotation_and_store(H, G, D, E, taps, rot, mode, dtype)
         last = n - 1
         tail = v_pages[pages[r][last // page_size], :, last % page_size + 1:]
         assert bool((tail == 0).all())
+
+
+@pytest.mark.parametrize("taps,C", [(4, 50), (2, 130), (3, 8)])
+def test_steps_of_single_rows_move_the_kept_inputs_themselves(taps, C):
+    """After a portion (with the kernel that moves the kept inputs), single rows with ``shift_single``: the
+    convolution of every row is what the whole sequence gives."""
+    from inferrs_b200 import kernels
+    g = torch.Generator().manual_seed(taps + C)
+    x = [torch.randn(9, C, generator=g), torch.randn(7, C, generator=g)]
+    wt = torch.randn(C, taps, generator=g)
+    want = [pr.causal_conv(t, wt) for t in x]
+    state = torch.zeros(3, (taps - 1) * C, device="cuda")
+    slots = dev([2, 0])
+    first = [2, 1]
+    q_start, row_request = requests_of(first)
+    rows = torch.cat([t[:n] for t, n in zip(x, first)]).cuda()
+    out = torch.empty(3, C, device="cuda")
+    kernels.causal_conv_rows(rows, 0, wt.cuda(), state, 0, dev(q_start), slots, dev(row_request), out, False)
+    kernels.conv_state_shift(rows, 0, C, taps, state, 0, dev(q_start), slots, 2)
+    got = [[out[:2].cpu()], [out[2:].cpu()]]
+    for i in range(6):
+        rows = torch.stack([x[0][2 + i], x[1][1 + i]]).cuda()
+        out = torch.empty(2, C, device="cuda")
+        kernels.causal_conv_rows(rows, 0, wt.cuda(), state, 0, dev([0, 1, 2]), slots, dev([0, 1]), out, False,
+                                 shift_single=True)
+        got[0].append(out[:1].cpu())
+        got[1].append(out[1:].cpu())
+    assert rel_err(torch.cat(got[0]), want[0][:8]) < 1e-5 and rel_err(torch.cat(got[1]), want[1][:7]) < 1e-5
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
