@@ -13,40 +13,86 @@
 // last taps - 1 inputs, oldest first, [taps - 1, C] floats at state_off of its slot (zeros for a new request).
 #include "common.cuh"
 
+#define CN_VEC (16 / (int)sizeof(act_t))
+struct alignas(16) CnActVec { act_t v[CN_VEC]; };
+template <typename T, int N> struct alignas(sizeof(T) * N >= 16 ? 16 : sizeof(T) * N) CnVec { T v[N]; };
+
+// N floats (a multiple of four) from or to an address that is a multiple of sixteen bytes
+template <int N> __device__ __forceinline__ void cn_load(float (&dst)[N], const float* src) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(src + i);
+        dst[i] = t.x; dst[i + 1] = t.y; dst[i + 2] = t.z; dst[i + 3] = t.w;
+    }
+}
+template <int N> __device__ __forceinline__ void cn_store(float* dst, const float (&src)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4)
+        *reinterpret_cast<float4*>(dst + i) = make_float4(src[i], src[i + 1], src[i + 2], src[i + 3]);
+}
+
 // ---------------------------------------------------------------------------
-// out[r, c] = add_input * x[r, col + c] + sum_j w[c, j] * input(r - (taps - 1 - j), c), c < C.  w [C, taps] float, the
-// last tap weighs the row itself.  shift_single (only for steps in which every request brings exactly one row): the
-// kernel also moves the kept inputs on by one place, so the state is ready for the next step.
+// out[r, c] = add_input * x[r, col + c] + sum_j w[j, c] * input(r - (taps - 1 - j), c), c < C.  w [taps, C] float
+// (tap-major, so that neighbouring channels' weights are neighbours), the last tap weighs the row itself.
+// shift_single (only for steps in which every request brings exactly one row): the kernel also moves the kept inputs
+// on by one place, so the state is ready for the next step.  VEC: sixteen bytes per thread and access.
 // ---------------------------------------------------------------------------
+template <bool VEC>
 __global__ void causal_conv_rows_kernel(const act_t* __restrict__ x, long ld, int col, int C, int taps,
                                         const float* __restrict__ w, float* __restrict__ state, long slot_stride,
                                         long state_off, const int* __restrict__ q_start, const int* __restrict__ slots,
                                         const int* __restrict__ row_request, act_t* __restrict__ out, long out_ld,
                                         int add_input, int shift_single) {
     ib_grid_dependency_sync();
+    constexpr int V = VEC ? CN_VEC : 1;
     const int row = blockIdx.y;
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
+    const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (c0 >= C) return;
     const int req = row_request[row];
     const int row0 = q_start[req];
     float* kept = taps > 1 ? state + (long)slots[req] * slot_stride + state_off : nullptr;
-    const float own = ib_to_float(x[(long)row * ld + col + c]);
-    float acc = add_input ? own : 0.0f;
+    float acc[V], own[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.0f;
     for (int j = 0; j < taps; ++j) {
         const int t = row - (taps - 1 - j);
-        float v;
-        if (t >= row0) v = ib_to_float(x[(long)t * ld + col + c]);
-        else v = kept[(long)(taps - 1 - (row0 - t)) * C + c];
-        acc = fmaf(w[(long)c * taps + j], v, acc);
+        float v[V], wv[V];
+        if (t >= row0) {
+            if constexpr (VEC) {
+                const CnActVec a = *reinterpret_cast<const CnActVec*>(x + (long)t * ld + col + c0);
+#pragma unroll
+                for (int i = 0; i < V; ++i) v[i] = ib_to_float(a.v[i]);
+            } else {
+                v[0] = ib_to_float(x[(long)t * ld + col + c0]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < V; ++i) v[i] = kept[(long)(taps - 1 - (row0 - t)) * C + c0 + i];
+        }
+        if constexpr (VEC) cn_load(wv, w + (long)j * C + c0); else wv[0] = w[(long)j * C + c0];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(wv[i], v[i], acc[i]);
+        if (j == taps - 1) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) own[i] = v[i];
+        }
     }
-    out[(long)row * out_ld + c] = ib_from_float<act_t>(acc);
-    // a step in which every request brings one row: the thread that has read the channel's kept inputs moves them
+    CnActVec o;
+#pragma unroll
+    for (int i = 0; i < V; ++i) o.v[i] = ib_from_float<act_t>(add_input ? acc[i] + own[i] : acc[i]);
+    if constexpr (VEC) *reinterpret_cast<CnActVec*>(out + (long)row * out_ld + c0) = o; else out[(long)row * out_ld + c0] = o.v[0];
+    // a step in which every request brings one row: the thread that has read the channels' kept inputs moves them
     // on by one place itself, and no kernel of its own has to follow
     if (shift_single && taps > 1) {
-        for (int k = 0; k + 1 < taps - 1; ++k) kept[(long)k * C + c] = kept[(long)(k + 1) * C + c];
-        kept[(long)(taps - 2) * C + c] = own;
+        for (int k = 0; k + 1 < taps - 1; ++k)
+#pragma unroll
+            for (int i = 0; i < V; ++i) kept[(long)k * C + c0 + i] = kept[(long)(k + 1) * C + c0 + i];
+#pragma unroll
+        for (int i = 0; i < V; ++i) kept[(long)(taps - 2) * C + c0 + i] = own[i];
     }
 }
+
+static inline bool cn_aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 IB_EXPORT int ib_causal_conv_rows(const void* x, long ld, int col, int C, int taps, const float* w, const float* state,
                                   long slot_stride, long state_off, const int* q_start, const int* slots,
@@ -57,10 +103,19 @@ IB_EXPORT int ib_causal_conv_rows(const void* x, long ld, int col, int C, int ta
         (taps > 1 && (state == nullptr || slot_stride < state_off + (long)(taps - 1) * C)))
         return IB_ERR_ARGUMENT;
     if (n_rows > 65535) return IB_ERR_UNSUPPORTED;
-    const int threads = C >= 256 ? 256 : ((C + 31) / 32) * 32;
-    ib_launch(causal_conv_rows_kernel, dim3((C + threads - 1) / threads, n_rows), threads, 0, stream, (const act_t*)x,
-              ld, col, C, taps, w, (float*)state, slot_stride, state_off, q_start, slots, row_request, (act_t*)out, out_ld,
-              add_input, shift_single);
+    const bool vec = C % CN_VEC == 0 && col % CN_VEC == 0 && ld % CN_VEC == 0 && out_ld % CN_VEC == 0 &&
+                     cn_aligned16(x) && cn_aligned16(out) && cn_aligned16(w);
+    const int units = vec ? C / CN_VEC : C;
+    const int threads = units >= 256 ? 256 : ((units + 31) / 32) * 32;
+    const dim3 grid((units + threads - 1) / threads, n_rows);
+    if (vec)
+        ib_launch(causal_conv_rows_kernel<true>, grid, threads, 0, stream, (const act_t*)x, ld, col, C, taps, w,
+                  (float*)state, slot_stride, state_off, q_start, slots, row_request, (act_t*)out, out_ld, add_input,
+                  shift_single);
+    else
+        ib_launch(causal_conv_rows_kernel<false>, grid, threads, 0, stream, (const act_t*)x, ld, col, C, taps, w,
+                  (float*)state, slot_stride, state_off, q_start, slots, row_request, (act_t*)out, out_ld, add_input,
+                  shift_single);
     return ib_launch_status();
 }
 
@@ -79,9 +134,6 @@ IB_EXPORT int ib_causal_conv_rows(const void* x, long ld, int col, int C, int ta
 // shift_single (only for steps in which every request brings exactly one row): the kernel also moves the kept inputs
 // on by one place, so that no kernel of its own has to follow.
 // ---------------------------------------------------------------------------
-#define CN_VEC (16 / (int)sizeof(act_t))
-struct alignas(16) CnActVec { act_t v[CN_VEC]; };
-
 template <typename WT, bool VEC>
 __global__ void conv_norm_rope_store_kernel(
     const act_t* __restrict__ proj, long ld, int H, int G, int D, int E, int taps, const float* __restrict__ conv_w,
@@ -129,12 +181,19 @@ __global__ void conv_norm_rope_store_kernel(
 #pragma unroll
                 for (int i = 0; i < V; ++i) own[i] = v[i];
             }
+            if (taps > 0) {
+                float wv[V];
+                if constexpr (VEC) cn_load(wv, conv_w + (long)j * C + c0); else wv[0] = conv_w[(long)j * C + c0];
 #pragma unroll
-            for (int i = 0; i < V; ++i) acc[i] = taps > 0 ? fmaf(conv_w[(long)j * C + c0 + i], v[i], acc[i]) : v[i];
+                for (int i = 0; i < V; ++i) acc[i] = fmaf(wv[i], v[i], acc[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] = v[i];
+            }
         }
+        if constexpr (VEC) cn_store(cn_row + c0, acc); else cn_row[c0] = acc[0];
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            cn_row[c0 + i] = acc[i];
             if (c0 + i < Cq) ssq += acc[i] * acc[i];
             else if (c0 + i < Cq + Ck) ssk += acc[i] * acc[i];
         }
@@ -151,12 +210,21 @@ __global__ void conv_norm_rope_store_kernel(
         ssq = ib_block_sum(ssq, red);
         ssk = ib_block_sum(ssk, red);
         const float inv_q = 1.0f / sqrtf(ssq / (float)Cq + eps), inv_k = 1.0f / sqrtf(ssk / (float)Ck + eps);
-        for (int c0 = threadIdx.x * V; c0 < Cq + Ck; c0 += blockDim.x * V)      // the thread that wrote the places reads them
+        for (int c0 = threadIdx.x * V; c0 < Cq + Ck; c0 += blockDim.x * V) {    // the thread that wrote the places reads them
+            const bool is_q = c0 < Cq;       // a thread's V numbers lie in one head, so in one projection
+            const float inv = is_q ? inv_q : inv_k;
+            const WT* wp = is_q ? q_weight + c0 : k_weight + (c0 - Cq);
+            if constexpr (VEC) {
+                const CnVec<WT, V> wv = *reinterpret_cast<const CnVec<WT, V>*>(wp);
+                float r[V];
+                cn_load(r, cn_row + c0);
 #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                const int c = c0 + i;
-                cn_row[c] *= c < Cq ? inv_q * ib_to_float(q_weight[c]) : inv_k * ib_to_float(k_weight[c - Cq]);
+                for (int i = 0; i < V; ++i) r[i] *= inv * ib_to_float(wv.v[i]);
+                cn_store(cn_row + c0, r);
+            } else {
+                cn_row[c0] *= inv * ib_to_float(wp[0]);
             }
+        }
         __syncthreads();
     } else if (norm_mode == 1) {
         __syncthreads();
@@ -186,13 +254,27 @@ __global__ void conv_norm_rope_store_kernel(
     for (int c0 = threadIdx.x * V; c0 < Cq + Ck; c0 += blockDim.x * V) {
         const int head = c0 / D, j0 = c0 - head * D;      // a thread's V numbers lie in one head
         CnActVec o;
+        if constexpr (VEC) {      // half is a multiple of V: the V numbers turn with V partners half a rotation away
+            float r[V];
+            cn_load(r, cn_row + c0);
+            if (j0 < rot_dim) {
+                const bool lower = j0 < half;
+                const int tj = lower ? j0 : j0 - half;
+                float partner[V], cv[V], sv[V];
+                cn_load(partner, cn_row + (lower ? c0 + half : c0 - half));
+                cn_load(cv, cs + tj);
+                cn_load(sv, sn + tj);
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const int c = c0 + i, j = j0 + i;
+                for (int i = 0; i < V; ++i) r[i] = lower ? r[i] * cv[i] - partner[i] * sv[i] : partner[i] * sv[i] + r[i] * cv[i];
+            }
+#pragma unroll
+            for (int i = 0; i < V; ++i) o.v[i] = ib_from_float<act_t>(r[i]);
+        } else {
+            const int c = c0, j = j0;
             float r = cn_row[c];
             if (j < half) r = r * cs[j] - cn_row[c + half] * sn[j];
             else if (j < rot_dim) r = cn_row[c - half] * sn[j - half] + r * cs[j - half];
-            o.v[i] = ib_from_float<act_t>(r);
+            o.v[0] = ib_from_float<act_t>(r);
         }
         act_t* dst = head < H ? q_out + ((long)row * H + head) * D + j0
                               : (kv_place >= 0 ? k_pages + (kv_place + (long)(head - H) * page_size) * D + j0 : nullptr);
@@ -203,8 +285,14 @@ __global__ void conv_norm_rope_store_kernel(
     for (int c0 = threadIdx.x * V; c0 < Cv; c0 += blockDim.x * V) {
         const int g = c0 / E, j0 = c0 - g * E;
         CnActVec o;
+        if constexpr (VEC) {
+            float r[V];
+            cn_load(r, cn_row + Cq + Ck + c0);
 #pragma unroll
-        for (int i = 0; i < V; ++i) o.v[i] = ib_from_float<act_t>(cn_row[Cq + Ck + c0 + i]);
+            for (int i = 0; i < V; ++i) o.v[i] = ib_from_float<act_t>(r[i]);
+        } else {
+            o.v[0] = ib_from_float<act_t>(cn_row[Cq + Ck + c0]);
+        }
         act_t* dst = v_pages + (kv_place + (long)g * page_size) * E + j0;
         if (VEC) *reinterpret_cast<CnActVec*>(dst) = o; else dst[0] = o.v[0];
     }
@@ -215,8 +303,6 @@ __global__ void conv_norm_rope_store_kernel(
         for (int j = threadIdx.x; j < behind; j += blockDim.x) dst[j] = ib_from_float<act_t>(0.0f);
     }
 }
-
-static inline bool cn_aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 IB_EXPORT int ib_conv_norm_rope_store(const void* proj, long ld, int n_rows, int H, int G, int D, int E, int taps,
                                       const float* conv_w, float* state, long slot_stride, long state_off,
@@ -241,7 +327,9 @@ IB_EXPORT int ib_conv_norm_rope_store(const void* proj, long ld, int n_rows, int
     if (smem > 200 * 1024) return IB_ERR_UNSUPPORTED;
     static IbDeviceSet sets[4];
     const bool vec = D % CN_VEC == 0 && E % CN_VEC == 0 && ld % CN_VEC == 0 && cn_aligned16(proj) &&
-                     cn_aligned16(q_out) && cn_aligned16(k_pages) && cn_aligned16(v_pages);
+                     cn_aligned16(q_out) && cn_aligned16(k_pages) && cn_aligned16(v_pages) &&
+                     (rot_dim / 2) % CN_VEC == 0 && cn_aligned16(conv_w) && cn_aligned16(cos_table) &&
+                     cn_aligned16(sin_table) && cn_aligned16(q_weight) && cn_aligned16(k_weight);
     const long units = vec ? C / CN_VEC : C;
     const int threads = units >= 512 ? 512 : (units >= 256 ? 256 : (units > 64 ? 128 : 64));
 #define IB_CNRS(WT, VEC, SET)                                                                                         \

@@ -1034,9 +1034,9 @@ def conv_state_shift(proj: torch.Tensor, conv_col: int, channels: int, taps: int
 def causal_conv_rows(x: torch.Tensor, col: int, conv_w: torch.Tensor, state: Optional[torch.Tensor], state_off: int,
                      q_start: torch.Tensor, slots: torch.Tensor, row_request: torch.Tensor, out: torch.Tensor,
                      add_input: bool, shift_single: bool = False):
-    """out[r, c] = (x[r, col + c] if ``add_input``) + sum_j conv_w[c, j] * input(r - (taps - 1 - j), c) for the
-    channels c < C = conv_w.shape[0]: a causal convolution per channel over a request's rows, the last tap weighing
-    the row itself.  input(t, c) is this step's row t of the same request, or what the request's slot of ``state``
+    """out[r, c] = (x[r, col + c] if ``add_input``) + sum_j conv_w[j, c] * input(r - (taps - 1 - j), c) for the
+    channels c < C = conv_w.shape[1]: a causal convolution per channel over a request's rows, ``conv_w`` [taps, C]
+    tap-major, the last tap weighing the row itself.  input(t, c) is this step's row t of the same request, or what the request's slot of ``state``
     keeps from earlier steps: its last taps - 1 inputs, oldest first, [taps - 1, C] float32 from ``state_off`` on
     (:func:`conv_state_shift` writes them after the step; zeros for a new request).  ``x`` is a [rows, ld] view in
     the activation dtype with unit last stride; ``out`` [rows, C].  ``shift_single``, only for steps in which every
@@ -1052,7 +1052,7 @@ def causal_conv_rows(x: torch.Tensor, col: int, conv_w: torch.Tensor, state: Opt
     if not (x.is_cuda and x.dtype == act and x.dim() == 2 and x.stride(1) == 1):
         raise KernelError(f"causal_conv_rows: x must be a CUDA [rows, ld] view in {act} with unit last stride")
     n = x.shape[0]
-    channels, taps = conv_w.shape
+    taps, channels = conv_w.shape
     if col < 0 or col + channels > x.shape[1] or out.shape != (n, channels) or row_request.shape[0] != n \
             or (taps > 1 and state is None):
         raise KernelError(f"causal_conv_rows: x {tuple(x.shape)}, columns {col}.., weights {tuple(conv_w.shape)}, out "

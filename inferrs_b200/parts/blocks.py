@@ -95,7 +95,7 @@ class InputConv:
         if spec.taps < 1:
             raise ValueError(f"a convolution has at least one tap, got {spec.taps}")
         self.spec = spec
-        self.weight = weights[spec.weight].to(torch.float32).contiguous()
+        self.weight = weights[spec.weight].to(torch.float32).t().contiguous()      # tap-major, as the kernel reads it
 
     @staticmethod
     def declare(spec) -> List[TensorDecl]:

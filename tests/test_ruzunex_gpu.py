@@ -488,7 +488,8 @@ def requests_of(lens):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("taps,C,add", [(4, 50, True), (1, 8, True), (2, 130, False), (5, 300, True)])
+@pytest.mark.parametrize("taps,C,add", [(4, 50, True), (1, 8, True), (2, 130, False), (5, 300, True), (4, 256, True),
+                                        (3, 1024, False)])
 def test_convolution_on_rows_with_its_state(taps, C, add, dtype):
     """Three requests in two steps (portions of 5, 1 and 2 rows after 7, 3 and 1): the second step reads what the
     state keeps of the first; a request shorter than the reach keeps the youngest of what it held."""
@@ -504,12 +505,13 @@ def test_convolution_on_rows_with_its_state(taps, C, add, dtype):
     for step, lens in enumerate((first, second)):
         q_start, row_request = requests_of(lens)
         rows = torch.cat([t[:first[r]] if step == 0 else t[first[r]:] for r, t in enumerate(x)])
-        pad = torch.randn(rows.shape[0], 3, generator=g)
+        lead = 8 if C % 8 == 0 else 3                               # sixteen bytes at a time where the sizes allow
+        pad = torch.randn(rows.shape[0], lead, generator=g)
         wide = act(torch.cat([pad, rows], dim=1), dtype)            # the rows as a slice of a wider tensor
         out = torch.empty(rows.shape[0], C, dtype=dtype, device="cuda")
-        kernels.causal_conv_rows(wide, 3, wt.cuda(), state if taps > 1 else None, 3, dev(q_start), slots,
-                                 dev(row_request), out, add)
-        kernels.conv_state_shift(wide, 3, C, taps, state, 3, dev(q_start), slots, 3)
+        kernels.causal_conv_rows(wide, lead, wt.t().contiguous().cuda(), state if taps > 1 else None, 3, dev(q_start),
+                                 slots, dev(row_request), out, add)
+        kernels.conv_state_shift(wide, lead, C, taps, state, 3, dev(q_start), slots, 3)
         for r in range(3):
             got[r].append(out[q_start[r]:q_start[r + 1]].float().cpu())
     tol = 1e-5 if dtype == torch.float32 else 2e-2
@@ -604,13 +606,13 @@ def test_steps_of_single_rows_move_the_kept_inputs_themselves(taps, C):
     q_start, row_request = requests_of(first)
     rows = torch.cat([t[:n] for t, n in zip(x, first)]).cuda()
     out = torch.empty(3, C, device="cuda")
-    kernels.causal_conv_rows(rows, 0, wt.cuda(), state, 0, dev(q_start), slots, dev(row_request), out, False)
+    kernels.causal_conv_rows(rows, 0, wt.t().contiguous().cuda(), state, 0, dev(q_start), slots, dev(row_request), out, False)
     kernels.conv_state_shift(rows, 0, C, taps, state, 0, dev(q_start), slots, 2)
     got = [[out[:2].cpu()], [out[2:].cpu()]]
     for i in range(6):
         rows = torch.stack([x[0][2 + i], x[1][1 + i]]).cuda()
         out = torch.empty(2, C, device="cuda")
-        kernels.causal_conv_rows(rows, 0, wt.cuda(), state, 0, dev([0, 1, 2]), slots, dev([0, 1]), out, False,
+        kernels.causal_conv_rows(rows, 0, wt.t().contiguous().cuda(), state, 0, dev([0, 1, 2]), slots, dev([0, 1]), out, False,
                                  shift_single=True)
         got[0].append(out[:1].cpu())
         got[1].append(out[1:].cpu())
