@@ -153,3 +153,56 @@ def make_weights(config: dict, seed: int, bare_second: bool = False) -> Dict[str
             t = r * (1.0 / d.shape[1] ** 0.5)
         out[n] = t.to(torch.bfloat16).to(torch.float32)
     return out
+
+
+def random_case(seed: int) -> dict:
+    """A configuration drawn from a seed: every size, count, window, constant and the order of layers differ from
+    draw to draw (head sizes that the tensor-core attention takes among them, and values that make mechanisms
+    degenerate)."""
+    import random
+    rnd = random.Random(seed)
+    pick = rnd.choice
+
+    def mlp():
+        kind = pick(["dense", "moe", "moe", None])
+        if kind == "dense":
+            return _dense(pick([20, 33, 64, 72]))
+        if kind == "moe":
+            experts = pick([1, 2, 3, 5, 8])
+            # a single choice among several is a close call in bfloat16 (see for_dtype): at least two are chosen
+            top = experts if experts <= 2 else rnd.randint(2, experts)
+            return _moe(pick([9, 16, 24, 40]), experts, top, pick([0.5, 1.0, 2.5]))
+        return None
+
+    def heads():
+        g = pick([1, 1, 2, 3])
+        return g * pick([1, 2, 3, 4]), g
+
+    def sizes():
+        d = pick([6, 8, 16, 24, 32, 64, 64, 128])
+        e = d if rnd.random() < 0.5 else pick([7, 12, 16, 40, 64])
+        return d, e
+
+    blend_sizes = (pick([1, 2, 3]), pick([12, 16, 40, 64]))      # layers that blend agree in their values' sizes
+    layers = []
+    for _ in range(rnd.randint(2, 6)):
+        if rnd.random() < 0.55:
+            h, g = heads()
+            d, e = sizes()
+            v_mix = pick([True, True, False, None])
+            if v_mix:
+                g, e = blend_sizes
+                h = g * pick([1, 2, 4])
+            layers.append(_attention(h, g, d, e, pick([0.1, 0.25, 0.4]), pick([None, 1, 2, 5, 17, 23, 33, 64, 70]),
+                                     v_mix, mlp()))
+        else:
+            h, g = heads()
+            d, e = sizes()
+            rot = None if rnd.random() < 0.25 else (pick([x for x in (2, 4, 6, 8, 16, 32, 64, 128) if x <= d]),
+                                                    pick([100.0, 10000.0, 500000.0]))
+            right = (pick([1, 2, 3, 5]), pick([6, 16, 20, 36, 128]), pick([5, 8, 12, 64]))
+            layers.append(_parallel(_left(h, g, d, e, pick([0.1, 0.2, 0.35]), pick([1, 2, 3, 4, 5]), rot), right,
+                                    pick([0.5, 1.0, 1.3]), pick([0.6, 1.0, 1.7]), mlp()))
+    return {"architecture": "Ruzunex", "vocab": pick([61, 97, 130, 257]), "width": pick([32, 48, 64, 90, 128]),
+            "norm": {"eps": pick([1e-5, 1e-6])}, "streams": pick([1, 2, 3, 4]), "canon": {"taps": pick([1, 2, 3, 4])},
+            "max_positions": 512, "layers": layers}

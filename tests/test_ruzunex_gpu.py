@@ -110,6 +110,31 @@ def test_whole_prompt_and_every_cutting_match_the_plain_statement(name, dtype):
     runner.manager.check_invariants()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("seed", list(range(16)))
+def test_configurations_drawn_at_random(seed, dtype):
+    """Sizes, counts, windows, constants and the order of layers drawn from a seed: a whole prompt, then the same
+    prompt in portions with its last tokens one by one, in a slot and pages that the first request has used."""
+    from ruzunex_cases import random_case
+    case = random_case(seed)
+    w = make_weights(case, 100 + seed)
+    toks = random_tokens(90, case["vocab"], seed=seed)
+    want = pr.forward(case, w, toks)
+    runner = make_runner(case, w, dtype, n_pages=8, max_requests=1)
+    runner.admit("whole")
+    assert_close(runner.step([entry("whole", toks)]), want, dtype)
+    runner.release("whole")
+    runner.admit("cut")
+    rows, at = [], 0
+    for n in cut(70, [19, 2, 33, 1, 5]):
+        rows.append(runner.step([entry("cut", toks[at:at + n])]))
+        at += n
+    for t in toks[70:]:
+        rows.append(runner.step([entry("cut", [t])]))
+    assert_close(torch.cat(rows), want, dtype)
+    runner.manager.check_invariants()
+
+
 def test_layer_sums_match_after_every_layer():
     """The sum of the streams after every layer, through the model's own blocks, in float32."""
     from inferrs_b200.engine.batch import build_context
