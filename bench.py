@@ -376,12 +376,15 @@ def design_bench(args) -> int:
                                                key_dim=128, value_dim=128)))
             # the left half of a parallel layer (every earlier key, a factor and a sink per head), the window attention
             # (a slope per head), the plain kernel they are built on, and the closest model's attention
+            tc = dict(att, impl="tcgen05")
             rows.append(microbench.attention(ns(form="prefill", batch=1, context=2048, tokens=2048, window=0,
-                                                per_head=True, heads=half, kv_heads=kv, **att)))
+                                                per_head=True, heads=half, kv_heads=kv, **tc)))
+            rows.append(microbench.attention(ns(form="prefill", batch=1, context=2048, tokens=2048, window=1024,
+                                                per_head=True, heads=heads, kv_heads=heads // 4, **tc)))
+            rows.append(microbench.attention(ns(form="prefill", batch=1, context=2048, tokens=2048, window=1024,
+                                                per_head=False, heads=heads, kv_heads=heads // 4, **tc)))
             rows.append(microbench.attention(ns(form="prefill", batch=1, context=2048, tokens=2048, window=1024,
                                                 per_head=True, heads=heads, kv_heads=heads // 4, **att)))
-            rows.append(microbench.attention(ns(form="prefill", batch=1, context=2048, tokens=2048, window=1024,
-                                                per_head=False, heads=heads, kv_heads=heads // 4, **att)))
             rows.append(microbench.joint(ns(form="prefill", impl="mma", batch=1, context=2048, tokens=2048, context_before=0,
                                             window=1024, splits=0, heads=half, kv_heads=kv, head_dim=128)))
             for b in (8, 64):

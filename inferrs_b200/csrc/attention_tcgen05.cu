@@ -57,8 +57,18 @@ struct Params {
     __nv_bfloat16* out;       // [N, n_heads * 128]
     int max_pages, page_size, n_pages, n_heads, n_kv_heads, window;
     float scale_log2;
+    // the form with a number per head (each array [n_heads] or absent): head h's scaled score is multiplied by
+    // head_scale[h], slopes[h] * (position - key) is taken off it, and exp(sinks[h]) joins the row's sum once
+    const float* head_scale;
+    const float* slopes;
+    const float* sinks;
 };
 
+#define FA_LOG2E 1.4426950408889634f
+
+// PER_HEAD: the scores are brought to their final form (factor, slope, mask) before the row's maximum is taken, so
+// a factor may have any sign; without it the maximum is taken over the raw products and scaled afterwards.
+template <bool PER_HEAD>
 __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v,
@@ -216,6 +226,13 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
         const bool row_valid = ti < n_tok;
         const int pos = row_valid ? p0 + ti : -1;
         const int lo = row_valid ? ib_first_visible(pos, P.window) : 0;
+        float sc2 = P.scale_log2, sl2 = 0.0f, sink2 = -INFINITY;
+        if (PER_HEAD) {
+            const int head = kvh * G + g;
+            if (P.head_scale) sc2 *= P.head_scale[head];
+            if (P.slopes) sl2 = P.slopes[head] * FA_LOG2E;
+            if (P.sinks) sink2 = P.sinks[head] * FA_LOG2E;
+        }
         float o[64];
 #pragma unroll
         for (int e = 0; e < 64; ++e) o[e] = 0.0f;
@@ -248,7 +265,19 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             // (four running maxima, and four running sums below: one chain of 64 dependent operations would
             // leave the two warps of a scheduler waiting on each other's latencies)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (all_visible) {
+            if (PER_HEAD) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int ka = key0 + j, kb = key0 + 32 + j;
+                    const float va = (all_visible || (ka >= lo && ka <= pos))
+                        ? fmaf(__uint_as_float(a[j]), sc2, -sl2 * (float)(pos - ka)) : -INFINITY;
+                    const float vb = (all_visible || (kb >= lo && kb <= pos))
+                        ? fmaf(__uint_as_float(b[j]), sc2, -sl2 * (float)(pos - kb)) : -INFINITY;
+                    a[j] = __float_as_uint(va);
+                    b[j] = __float_as_uint(vb);
+                    mx4[j & 3] = fmaxf(mx4[j & 3], fmaxf(va, vb));
+                }
+            } else if (all_visible) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j)
                     mx4[j & 3] = fmaxf(mx4[j & 3], fmaxf(__uint_as_float(a[j]), __uint_as_float(b[j])));
@@ -268,7 +297,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             float* xb = xchg + (i & 1) * 256;
             xb[ch * 128 + r] = mx;
             pair_sync(warp & 3);
-            mx = fmaxf(mx, xb[(ch ^ 1) * 128 + r]) * P.scale_log2;
+            mx = PER_HEAD ? fmaxf(mx, xb[(ch ^ 1) * 128 + r]) : fmaxf(mx, xb[(ch ^ 1) * 128 + r]) * P.scale_log2;
             const float m_new = fmaxf(m, mx);
             const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
             const float corr = m == -INFINITY ? 0.0f : ex2(m - m_safe);
@@ -281,7 +310,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
                 for (int j = 0; j < 8; ++j) {
                     const int e = 8 * c + j;
                     const float x = __uint_as_float(e < 32 ? a[e] : b[e - 32]);
-                    p[j] = ex2(fmaf(x, P.scale_log2, -m_safe));   // exp2(-inf) = 0 for keys that are not seen
+                    p[j] = PER_HEAD ? ex2(x - m_safe) : ex2(fmaf(x, P.scale_log2, -m_safe));   // exp2(-inf) = 0 for keys that are not seen
                     sum4[j & 3] += p[j];
                 }
                 uint4 w;
@@ -321,7 +350,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
         pair_sync(warp & 3);
         l += xb[(ch ^ 1) * 128 + r];
         if (row_valid && ok) {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            if (PER_HEAD && sink2 > -INFINITY) {     // the place without a key joins the denominator
+                const float m_new = fmaxf(m, sink2);
+                const float f = m == -INFINITY ? 0.0f : ex2(m - m_new);
+                inv = f / (l * f + ex2(sink2 - m_new));
+            }
             __nv_bfloat16* dst = P.out + ((long)(row0 + ti) * P.n_heads + kvh * G + g) * D + ch * 64;
 #pragma unroll
             for (int c0 = 0; c0 < 64; c0 += 8) {
@@ -348,12 +382,14 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
 }  // namespace fa
 
 // Prefill-form attention for head size 128, bfloat16: tile i holds up to 128/G tokens of request tile_req[i]
-// from row tile_row0[i].  Same arguments and results as ib_paged_attention_mma with decode_form = 0.
-IB_EXPORT int ib_paged_attention_tcgen05(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
-                                         int max_pages, int page_size, int n_pages, const int* tile_req,
-                                         const int* tile_row0, int n_tiles, const int* q_start, const int* positions,
-                                         int n_rows, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
-                                         void* out, cudaStream_t stream) {
+// from row tile_row0[i].  Same arguments and results as ib_paged_attention_mma with decode_form = 0 (head_scale,
+// slopes and sinks, [n_heads] each, may be absent: with all three absent the form without them runs).
+static int attention_tcgen05_launch(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                    int max_pages, int page_size, int n_pages, const int* tile_req,
+                                    const int* tile_row0, int n_tiles, const int* q_start, const int* positions,
+                                    int n_rows, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                    void* out, const float* head_scale, const float* slopes, const float* sinks,
+                                    cudaStream_t stream) {
     if (n_tiles <= 0) return IB_OK;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || page_size <= 0 || max_pages <= 0) return IB_ERR_ARGUMENT;
     const int G = n_heads / n_kv_heads;
@@ -388,12 +424,41 @@ IB_EXPORT int ib_paged_attention_tcgen05(const void* q, const void* k_pages, con
     P.block_table = block_table; P.tile_req = tile_req; P.tile_row0 = tile_row0; P.q_start = q_start;
     P.positions = positions; P.out = (__nv_bfloat16*)out; P.max_pages = max_pages; P.page_size = page_size;
     P.n_pages = n_pages; P.n_heads = n_heads; P.n_kv_heads = n_kv_heads; P.window = window;
-    P.scale_log2 = scale * 1.4426950408889634f;
+    P.scale_log2 = scale * FA_LOG2E;
+    P.head_scale = head_scale; P.slopes = slopes; P.sinks = sinks;
     const size_t smem = 7 * fa::TILE_BYTES + 18 * 8 + 4 * 128 * 4 + fa::SMEM_SLACK;
-    static IbDeviceSet configured;   // the attribute is kept per device
-    if (const int e = ib_allow_dynamic_smem(configured, fa::attention_kernel, smem)) return e;
-    ib_launch(fa::attention_kernel, dim3(n_tiles * n_kv_heads), fa::THREADS, smem, stream, mq, mk, mv, P);
+    static IbDeviceSet configured, configured_per_head;   // the attribute is kept per device
+    if (head_scale != nullptr || slopes != nullptr || sinks != nullptr) {
+        if (const int e = ib_allow_dynamic_smem(configured_per_head, fa::attention_kernel<true>, smem)) return e;
+        ib_launch(fa::attention_kernel<true>, dim3(n_tiles * n_kv_heads), fa::THREADS, smem, stream, mq, mk, mv, P);
+        return ib_launch_status();
+    }
+    if (const int e = ib_allow_dynamic_smem(configured, fa::attention_kernel<false>, smem)) return e;
+    ib_launch(fa::attention_kernel<false>, dim3(n_tiles * n_kv_heads), fa::THREADS, smem, stream, mq, mk, mv, P);
     return ib_launch_status();
+}
+
+IB_EXPORT int ib_paged_attention_tcgen05(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+                                         int max_pages, int page_size, int n_pages, const int* tile_req,
+                                         const int* tile_row0, int n_tiles, const int* q_start, const int* positions,
+                                         int n_rows, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                         void* out, cudaStream_t stream) {
+    return attention_tcgen05_launch(q, k_pages, v_pages, block_table, max_pages, page_size, n_pages, tile_req, tile_row0,
+                                    n_tiles, q_start, positions, n_rows, n_heads, n_kv_heads, head_dim, scale, window, out,
+                                    nullptr, nullptr, nullptr, stream);
+}
+
+// The same with a factor, a slope and a sink per head (each [n_heads] floats or absent).
+IB_EXPORT int ib_paged_attention_tcgen05_per_head(const void* q, const void* k_pages, const void* v_pages,
+                                                  const int* block_table, int max_pages, int page_size, int n_pages,
+                                                  const int* tile_req, const int* tile_row0, int n_tiles,
+                                                  const int* q_start, const int* positions, int n_rows, int n_heads,
+                                                  int n_kv_heads, int head_dim, float scale, int window, void* out,
+                                                  const float* head_scale, const float* slopes, const float* sinks,
+                                                  cudaStream_t stream) {
+    return attention_tcgen05_launch(q, k_pages, v_pages, block_table, max_pages, page_size, n_pages, tile_req, tile_row0,
+                                    n_tiles, q_start, positions, n_rows, n_heads, n_kv_heads, head_dim, scale, window, out,
+                                    head_scale, slopes, sinks, stream);
 }
 
 IB_EXPORT int ib_attention_tcgen05_error(int reset) {
@@ -417,6 +482,13 @@ IB_EXPORT int ib_attention_tcgen05_error_async(int* out, cudaStream_t stream) {
 IB_EXPORT int ib_paged_attention_tcgen05(const void*, const void*, const void*, const int*, int, int, int, const int*,
                                          const int*, int, const int*, const int*, int, int, int, int, float, int, void*,
                                          cudaStream_t) {
+    return IB_ERR_UNSUPPORTED;
+}
+
+IB_EXPORT int ib_paged_attention_tcgen05_per_head(const void*, const void*, const void*, const int*, int, int, int,
+                                                  const int*, const int*, int, const int*, const int*, int, int, int, int,
+                                                  float, int, void*, const float*, const float*, const float*,
+                                                  cudaStream_t) {
     return IB_ERR_UNSUPPORTED;
 }
 

@@ -53,6 +53,9 @@ _SIGNATURES = {
     "ib_paged_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                    c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                    c_void_p],
+    "ib_paged_attention_tcgen05_per_head": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+                                            c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "ib_attention_tcgen05_error": [c_int],
     "ib_paged_attention_pair_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                         c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
@@ -1546,10 +1549,18 @@ def tcgen05_attention_supported(dtype: torch.dtype, n_heads: int, n_kv_heads: in
 
 def paged_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                             tile_req: torch.Tensor, tile_row0: torch.Tensor, n_tiles: int, q_start: torch.Tensor,
-                            positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor):
+                            positions: torch.Tensor, scale: float, window: Optional[int], out: torch.Tensor,
+                            head_scale: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                            sinks: Optional[torch.Tensor] = None):
     """Attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 128): tile i holds up to
-    128/G tokens of request tile_req[i] from row tile_row0[i]; Q, K, V by TMA, scores and P V in tensor memory."""
+    128/G tokens of request tile_req[i] from row tile_row0[i]; Q, K, V by TMA, scores and P V in tensor memory.
+    ``head_scale`` / ``slopes`` / ``sinks`` (float32 [H]): as in :func:`paged_attention_generic`; with any of them the
+    kernel's form runs that brings the scores to their final form before it takes the row's maximum."""
     bf = (torch.bfloat16,)
+    for name, t in (("head_scale", head_scale), ("slopes", slopes), ("sinks", sinks)):
+        _need(t, name, (torch.float32,), 1, optional=True)
+        if t is not None and t.shape[0] != q.shape[1]:
+            raise KernelError(f"paged_attention_tcgen05: {name} has {t.shape[0]} numbers for {q.shape[1]} heads")
     _need(q, "q", bf, 3)
     _need(k_pages, "k_pages", bf, 4)
     _need(v_pages, "v_pages", bf, 4)
@@ -1564,6 +1575,13 @@ def paged_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     if not tcgen05_attention_supported(q.dtype, nh, nkv, d, page_size):
         raise KernelError(f"paged_attention_tcgen05 takes head_dim 128, a page size of 8..128 that divides 128 and a "
                           f"group size of at most 128; got head_dim {d}, page size {page_size}, {nh}/{nkv} heads")
+    if head_scale is not None or slopes is not None or sinks is not None:
+        _check(_core(torch.bfloat16).ib_paged_attention_tcgen05_per_head(
+            _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
+            _p(tile_row0), n_tiles, _p(q_start), _p(positions), n, nh, nkv, d, float(scale),
+            int(window) if window else 0, _p(out), _p(head_scale), _p(slopes), _p(sinks), _stream()),
+            "paged_attention_tcgen05")
+        return
     _check(_core(torch.bfloat16).ib_paged_attention_tcgen05(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, n_pages, _p(tile_req),
         _p(tile_row0), n_tiles, _p(q_start), _p(positions), n, nh, nkv, d, float(scale), int(window) if window else 0,
@@ -1635,8 +1653,9 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
 
     ``ctx`` is the step's :class:`~inferrs_b200.engine.batch.StepContext` (row_request, positions
     and what the faster kernels need to cut the work).  ``head_scale`` / ``slopes`` / ``sinks`` (float32 [H], see
-    :func:`paged_attention_generic`): scores with any of them go to the ``mma.sync`` kernel where it takes the sizes
-    and to the float32 kernel otherwise.
+    :func:`paged_attention_generic`): scores with any of them go to the tcgen05 kernel's per-head form (prompt
+    portions, head size 128), to the ``mma.sync`` kernel (steps of single tokens; head sizes 64 and 256) where these
+    take the sizes, and to the float32 kernel otherwise.
     """
     n, nh, d = q.shape
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
@@ -1651,6 +1670,11 @@ def paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                                    else ctx.max_kv_len)
             paged_attention_mma(q, k_pages, v_pages, block_table, ctx.row_request, ctx.q_start, ctx.n_requests,
                                 ctx.q_start, ctx.positions, scale, window, out, True, splits, **per_head)
+        elif tcgen05_attention_supported(q.dtype, nh, nkv, d, page_size) and scale > 0:
+            # prompt portions (and what single tokens stand beside them) on the tcgen05 kernel's per-head form
+            tile_req, tile_row0, n_tiles = ctx.attention_tiles(TC_ROWS // (nh // nkv))
+            paged_attention_tcgen05(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,
+                                    ctx.positions, scale, window, out, **per_head)
         else:
             tile_req, tile_row0, n_tiles = ctx.attention_tiles(MMA_KEYS // (nh // nkv))
             paged_attention_mma(q, k_pages, v_pages, block_table, tile_req, tile_row0, n_tiles, ctx.q_start,

@@ -103,9 +103,9 @@ def attention(args) -> dict:
     scale = d ** -0.5
     window = getattr(args, "window", 0) or None
     per_head = {}
-    if getattr(args, "per_head", False):       # a factor, a slope and a sink per head (the ``mma.sync`` kernel only)
-        if args.impl != "mma":
-            raise SystemExit("--per-head is an option of --impl mma")
+    if getattr(args, "per_head", False):       # a factor, a slope and a sink per head
+        if args.impl not in ("mma", "tcgen05") or (args.impl == "tcgen05" and args.form == "decode"):
+            raise SystemExit("--per-head is an option of --impl mma and of the prefill form of --impl tcgen05")
         per_head = {"head_scale": 1.0 + 0.1 * torch.randn(nh, device=dev),
                     "slopes": torch.tensor([2.0 ** (-8.0 * (h + 1) / nh) for h in range(nh)], device=dev),
                     "sinks": torch.randn(nh, device=dev)}
@@ -132,7 +132,7 @@ def attention(args) -> dict:
         tile_row0 = torch.tensor(row0, dtype=torch.int32, device=dev)
         if args.impl == "tcgen05":
             fn = lambda: kernels.paged_attention_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
-                                                         q_start, positions, scale, window, out)
+                                                         q_start, positions, scale, window, out, **per_head)
         elif args.impl == "tcgen05-pair":
             fn = lambda: kernels.paged_attention_pair_tcgen05(q, k_pages, v_pages, table, tile_req, tile_row0, len(req),  # noqa: E731
                                                               q_start, positions, scale, window, out)

@@ -799,6 +799,38 @@ def test_tensor_core_decode_form_cut_into_slices_adds_the_sink_once(H, G, D, win
     assert rel_err(out.float(), want) < 2e-2
 
 
+@pytest.mark.parametrize("H,G,window,opts,start", [(8, 2, 100, "tbs", 0), (4, 4, None, "ts", 0), (6, 1, 37, "b", 0),
+                                                   (3, 3, None, "s", 0), (16, 2, 300, "tbs", 0), (8, 2, 129, "tb", 333),
+                                                   (5, 5, None, "tbs", 77)])
+def test_tcgen05_prefill_form_with_a_factor_a_slope_and_a_sink_per_head(H, G, window, opts, start):
+    """The tcgen05 kernel's per-head form alone, head size 128: a prompt from position 0, and a portion behind keys
+    that earlier steps left (tiles of the request's later rows; a negative factor among the heads)."""
+    from inferrs_b200 import kernels
+    g = torch.Generator().manual_seed(H * 10 + G)
+    D, n = 128, 333
+    T = start + n
+    q = torch.randn(n, H, D, generator=g).to(torch.bfloat16).float()
+    k = torch.randn(T, G, D, generator=g).to(torch.bfloat16).float()
+    v = torch.randn(T, G, D, generator=g).to(torch.bfloat16).float()
+    temp = (1.0 + 0.3 * torch.randn(H, generator=g)) if "t" in opts else None
+    if temp is not None:
+        temp[0] = -0.7
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)]) if "b" in opts else None
+    sink = 2.0 * torch.randn(H, generator=g) if "s" in opts else None
+    scale = 1.0 / math.sqrt(D)
+    want = plain_scored_attention(q, k, v, torch.arange(start, T), scale, window, temp, slopes, sink).flatten(1)
+    k_pages, v_pages, table = paged(k, v, 16, torch.bfloat16, 7)
+    tpt = kernels.TC_ROWS // (H // G)
+    row0 = list(range(0, n, tpt))
+    out = torch.empty(n, H * D, dtype=torch.bfloat16, device="cuda")
+    f = lambda t: None if t is None else t.float().cuda().contiguous()      # noqa: E731
+    kernels.paged_attention_tcgen05(act(q, torch.bfloat16), k_pages, v_pages, table, dev([0] * len(row0)), dev(row0),
+                                    len(row0), dev([0, n]), dev(list(range(start, T))), scale, window, out,
+                                    head_scale=f(temp), slopes=f(slopes), sinks=f(sink))
+    assert kernels.attention_tcgen05_error() == 0
+    assert rel_err(out.float(), want) < 2e-2
+
+
 @pytest.mark.parametrize("experts,top", [(8, 3), (5, 2), (3, 3), (70, 6), (4, 1), (1, 1)])
 def test_router_by_shares_of_the_softmax_over_all(experts, top):
     from inferrs_b200 import kernels
