@@ -22,6 +22,8 @@
 #include <cuda.h>
 
 #include "common.cuh"
+
+#include <type_traits>
 #include "sm100.cuh"
 
 #if IB_ACT_BF16
@@ -266,16 +268,33 @@ __global__ void __launch_bounds__(THREADS, 1) attention_kernel(const __grid_cons
             // leave the two warps of a scheduler waiting on each other's latencies)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (PER_HEAD) {
+                // key0 + j lies (pos - key0) - j behind the row: its slope's share is base + sl2 * j, with j a constant
+                // of the unrolled loop, so no position is converted per key
+                const float base = -sl2 * (float)(pos - key0);
+                auto fill = [&](auto with_slope, auto with_mask) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int ka = key0 + j, kb = key0 + 32 + j;
-                    const float va = (all_visible || (ka >= lo && ka <= pos))
-                        ? fmaf(__uint_as_float(a[j]), sc2, -sl2 * (float)(pos - ka)) : -INFINITY;
-                    const float vb = (all_visible || (kb >= lo && kb <= pos))
-                        ? fmaf(__uint_as_float(b[j]), sc2, -sl2 * (float)(pos - kb)) : -INFINITY;
-                    a[j] = __float_as_uint(va);
-                    b[j] = __float_as_uint(vb);
-                    mx4[j & 3] = fmaxf(mx4[j & 3], fmaxf(va, vb));
+                    for (int j = 0; j < 32; ++j) {
+                        float va = decltype(with_slope)::value ? fmaf(__uint_as_float(a[j]), sc2, fmaf(sl2, (float)j, base))
+                                                               : __uint_as_float(a[j]) * sc2;
+                        float vb = decltype(with_slope)::value
+                                       ? fmaf(__uint_as_float(b[j]), sc2, fmaf(sl2, (float)(32 + j), base))
+                                       : __uint_as_float(b[j]) * sc2;
+                        if (decltype(with_mask)::value) {
+                            const int ka = key0 + j, kb = key0 + 32 + j;
+                            if (!(ka >= lo && ka <= pos)) va = -INFINITY;
+                            if (!(kb >= lo && kb <= pos)) vb = -INFINITY;
+                        }
+                        a[j] = __float_as_uint(va);
+                        b[j] = __float_as_uint(vb);
+                        mx4[j & 3] = fmaxf(mx4[j & 3], fmaxf(va, vb));
+                    }
+                };
+                using Yes = std::integral_constant<bool, true>;
+                using No = std::integral_constant<bool, false>;
+                if (sl2 != 0.0f) {
+                    if (all_visible) fill(Yes{}, No{}); else fill(Yes{}, Yes{});
+                } else {
+                    if (all_visible) fill(No{}, No{}); else fill(No{}, Yes{});
                 }
             } else if (all_visible) {
 #pragma unroll
