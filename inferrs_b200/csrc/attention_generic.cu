@@ -20,8 +20,8 @@
 //
 // Three more options, each a number per head (absent: not applied).  head_scale[h] multiplies head h's scaled score
 // (a learned temperature).  slopes[h] * (pos - j) is taken off the score (a bias that grows linearly with the
-// distance).  sinks[h]: the softmax's denominator also holds exp(sinks[h]), a place without key and value that
-// counts once per row; it is neither scaled nor biased.
+// distance).  sinks[h]: every row's softmax gets one more term, exp(sinks[h]), in its denominator only; no key or
+// value belongs to it, and neither the scale nor the factor nor the slope touches it.
 #include "common.cuh"
 
 #define ATT_WARPS 4

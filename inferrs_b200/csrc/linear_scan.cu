@@ -7,7 +7,7 @@
 //       m_t = max(f_t + m_{t-1}, i_t)
 //       S_t = exp(f_t + m_{t-1} - m_t) S_{t-1} + exp(i_t - m_t) k_t v_t^T        (n_t the same with k_t alone)
 //       o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
-//   mode 2, a forget gate per key channel that also decides what is written (HGRN2):
+//   mode 2, a forget gate per key channel whose complement takes the key's place (HGRN2):
 //       f_t = l + (1 - l) sigmoid(z_t + b),   S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T,   o_t = S_t^T silu(q_t)
 //       l is a lower bound per channel; there is no key: what the gate lets go is what the value fills
 //

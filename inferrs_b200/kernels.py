@@ -649,8 +649,8 @@ def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     the table reads its last entry).
 
     ``head_scale`` / ``slopes`` / ``sinks``: float32 [H] each.  Head h's scaled score is multiplied by head_scale[h];
-    slopes[h] * (pos - j) is taken off it; the softmax's denominator also holds exp(sinks[h]) (a place without key
-    and value that counts once, neither scaled nor biased)."""
+    slopes[h] * (pos - j) is taken off it; every row's softmax gets one more term, exp(sinks[h]), in its denominator
+    only (no key or value belongs to it; scale, factor and slope leave it alone)."""
     act = out.dtype
     _need(q, "q", (act,), 3)
     for name, t in (("head_scale", head_scale), ("slopes", slopes), ("sinks", sinks)):

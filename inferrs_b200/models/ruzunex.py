@@ -11,7 +11,7 @@ config.json values:
   of the first layer that says ``v_mix``, a sigmoid gate on the heads) or "parallel": two mixers side by side on the
   same input, summed with two scales.  Left: attention behind short convolutions on q, k and v, norms over the whole
   projection, a partial rotation, a learned factor per head on the scores, every earlier key visible and a sink in
-  the softmax.  Right: HGRN2, linear attention whose forget gate also decides what is written;
+  the softmax.  Right: HGRN2, a linear recurrence whose key is the complement of its forget gate;
 * the feed-forward is a gated dense one with the tanh form of gelu, or routed experts with a clamped activation,
   chosen by their softmax scores over all experts and weighed by their share of the chosen scores;
 * tensors: ``embed``, ``l<i>.norm1|norm2``, ``l<i>.canon1|canon2``, ``l<i>.hc1|hc2.in|out|mix``, ``l<i>.mix.*``,

@@ -82,8 +82,8 @@ class AttentionSpec:
 
     ``distance_slopes`` (one constant per head): slope_h (i - j) is taken off head h's scaled score.
     ``head_scale`` [n_heads]: head h's scaled score is multiplied by a learned number.
-    ``sink`` [n_heads]: the softmax's denominator also holds exp(sink_h), a place without key and value that counts
-    once; it is neither scaled nor biased.
+    ``sink`` [n_heads]: every row's softmax gets one more term, exp(sink_h), in its denominator only; no key or value
+    belongs to it, and ``scale``, ``head_scale`` and the distance terms leave it alone.
     ``qkv_conv`` = (q, k, v tensor names, each [channels, ``conv_taps``]): a causal convolution per channel directly
     behind each projection (the last tap weighs the token itself, zeros before the start, no bias, no activation);
     the last conv_taps - 1 projected rows of a request belong to its state.
@@ -331,7 +331,7 @@ class ChannelDecayScanSpec:
 
 @dataclass(frozen=True)
 class ForgetWriteScanSpec:
-    """HGRN2: linear attention whose forget gate also decides what is written.  Per head a matrix state S
+    """HGRN2: a linear recurrence whose key is the complement of its forget gate.  Per head a matrix state S
     [key_dim, value_dim]: f = l + (1 - l) sigmoid(f_proj(x) + f_bias) per key channel with a learned lower bound l
     (``lower`` [n_heads * key_dim]); S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T, o_t = S_t^T q_t with
     q = silu(q_proj(x)) and v = v_proj(x); there is no key and no other scale.  Each head's o is divided by its root
@@ -425,9 +425,11 @@ class StreamConnectionSpec:
 
 @dataclass(frozen=True)
 class InputConvSpec:
-    """What a sub-layer reads, h (its norm's output), is replaced by h + conv(h): a causal convolution over time on
-    each channel, conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j) with zeros before the sequence's start.  ``weight``
-    names the tensor [width, taps] (no bias).  The last taps - 1 inputs h of a request belong to its state."""
+    """A short convolution over time between a sub-layer's norm and its part.  With h the norm's output [rows, width],
+    the part is handed h + c(h), where c works on every channel by itself:
+    c(h)_t = sum_{j < taps} weight[:, j] * h_(t - (taps - 1 - j)); rows that would lie ahead of a request's first token
+    count as zero.  ``weight`` names the tensor [width, taps] (the last column multiplies the row itself; no bias).  A
+    request's state keeps the taps - 1 most recent rows of h, so that a later step can go on where this one ended."""
 
     width: int
     taps: int

@@ -151,7 +151,7 @@ def forget_write_rule(q, f, v, S=None) -> torch.Tensor:
 
 
 def forget_write_mixer(h, m: dict, w: Dict[str, torch.Tensor], p: str, eps: float) -> torch.Tensor:
-    """The right half of the mixer "parallel": a forget gate with a learned lower bound that also decides what is
+    """The right half of the mixer "parallel": a forget gate with a learned lower bound whose complement says what is
     written; every head's result normed over its value size with one shared weight."""
     T = h.shape[0]
     H, D, E = int(m["heads"]), int(m["dim"]), int(m["vdim"])
