@@ -144,7 +144,7 @@ __global__ void conv_norm_rope_store_kernel(
     int page_size, int n_pages, act_t* __restrict__ k_pages, act_t* __restrict__ v_pages, act_t* __restrict__ q_out,
     int shift_single) {
     extern __shared__ __align__(16) float cn_row[];
-    __shared__ float red[32];
+    __shared__ float red[64];
     ib_grid_dependency_sync();
     constexpr int V = VEC ? CN_VEC : 1;
     const int row = blockIdx.x;
@@ -207,8 +207,15 @@ __global__ void conv_norm_rope_store_kernel(
     }
     // 2. the norms
     if (norm_mode == 2) {
-        ssq = ib_block_sum(ssq, red);
-        ssk = ib_block_sum(ssk, red);
+        {   // the two sums of squares over the block at once: one meeting instead of two
+            const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+            ssq = ib_warp_sum(ssq);
+            ssk = ib_warp_sum(ssk);
+            if (lane == 0) { red[warp] = ssq; red[32 + warp] = ssk; }
+            __syncthreads();
+            ssq = ib_warp_sum(lane < n_warps ? red[lane] : 0.0f);
+            ssk = ib_warp_sum(lane < n_warps ? red[32 + lane] : 0.0f);
+        }
         const float inv_q = 1.0f / sqrtf(ssq / (float)Cq + eps), inv_k = 1.0f / sqrtf(ssk / (float)Ck + eps);
         for (int c0 = threadIdx.x * V; c0 < Cq + Ck; c0 += blockDim.x * V) {    // the thread that wrote the places reads them
             const bool is_q = c0 < Cq;       // a thread's V numbers lie in one head, so in one projection

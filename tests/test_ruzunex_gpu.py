@@ -546,14 +546,16 @@ def test_convolution_on_rows_with_its_state(taps, C, add, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,D,E,taps,rot,mode", [(6, 2, 24, 20, 3, 12, 2), (1, 1, 16, 64, 1, 0, 2), (4, 4, 16, 40, 2, 16, 2),
-                                                  (3, 1, 10, 7, 5, 6, 1), (8, 2, 128, 128, 4, 64, 2), (2, 2, 8, 8, 0, 4, 0)])
+                                                  (3, 1, 10, 7, 5, 6, 1), (8, 2, 128, 128, 4, 64, 2), (2, 2, 8, 8, 0, 4, 0),
+                                                  (2, 1, 16, 8, 3, 8, 2), (3, 1, 10, 6, 4, 4, 1)])
 def test_convolution_norm_rotation_and_store(H, G, D, E, taps, rot, mode, dtype):
     """One pass over q | k | v of two requests in two steps against the plain functions: the convolution (with its
     state), the norm over the whole projection (or per head, or none), the partial rotation, q dense, k and v in
     their pages at the rows' positions."""
     from inferrs_b200 import kernels
     g = torch.Generator().manual_seed(H * 1000 + D)
-    first, second = [21, 3], [14, 1]
+    # the last two cases: more than a thousand rows in a step, where a block takes several rows one after the other
+    first, second = ([1100, 30], [10, 1]) if (D, E) in ((16, 8), (10, 6)) else ([21, 3], [14, 1])
     Cq, Ck, Cv = H * D, G * D, G * E
     C = Cq + Ck + Cv
     x = [torch.randn(a + b, C + 5, generator=g).to(torch.bfloat16).float() for a, b in zip(first, second)]
@@ -577,12 +579,16 @@ def test_convolution_norm_rotation_and_store(H, G, D, E, taps, rot, mode, dtype)
         want_q.append(q)
         want_k.append(k)
         want_v.append(v.reshape(n, G, E))
-    page_size, n_pages = 16, 8
+    page_size = 16
+    need = [(a + b + page_size - 1) // page_size for a, b in zip(first, second)]
+    n_pages = sum(need) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    pages = [order[:need[0]], order[need[0]:need[0] + need[1]]]
     k_pages = torch.full((n_pages, G, page_size, D), float("nan"), dtype=dtype, device="cuda")
     v_pages = torch.full((n_pages, G, page_size, E), float("nan"), dtype=dtype, device="cuda")
-    table = dev([[5, 2, 7, -1], [1, 6, -1, -1]])
+    table = dev([p + [-1] * (max(need) + 1 - len(p)) for p in pages])
     half = rot // 2
-    ang = torch.arange(64, dtype=torch.float32)[:, None] * (base ** (-2.0 * torch.arange(max(half, 1), dtype=torch.float64) / max(rot, 1))).float()[None, :]
+    ang = torch.arange(max(64, sum(first) + sum(second)), dtype=torch.float32)[:, None] * (base ** (-2.0 * torch.arange(max(half, 1), dtype=torch.float64) / max(rot, 1))).float()[None, :]
     cos, sin = torch.cos(ang).cuda().contiguous(), torch.sin(ang).cuda().contiguous()
     state = torch.zeros(3, max(taps - 1, 0) * C + 1, device="cuda")
     slots = dev([1, 0])
@@ -602,7 +608,6 @@ def test_convolution_norm_rotation_and_store(H, G, D, E, taps, rot, mode, dtype)
         for r in range(2):
             got_q[r].append(q_out[q_start[r]:q_start[r + 1]].float().cpu())
     tol = 2e-5 if dtype == torch.float32 else 3e-2
-    pages = [[5, 2, 7], [1, 6]]
     for r in range(2):
         wq_r = want_q[r] if dtype == torch.float32 else want_q[r]
         assert rel_err(torch.cat(got_q[r]).flatten(1), wq_r.flatten(1)) < tol
